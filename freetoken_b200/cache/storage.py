@@ -1,0 +1,71 @@
+"""Device memory behind the cache manager.
+
+One tensor per page group, ``[stops, 2 (K,V), pages, kv_heads, page_size,
+head_dim]``: a page of one KV head is ``page_size * head_dim`` contiguous
+elements, which is the tile attention kernels stream.  (The reference's pool is
+``[2, layers, pages, page_size, kv_heads, head_dim]``,
+python/freetoken/kvcache/mha_pool.py:50-58.)  Page 0 is the sink that unused
+block-table entries point at.  State groups are ``[stops, slots + 1, *shape]``
+with the last row as the sink for padded rows
+(cf. python/freetoken/kvcache/linear_state_pool.py:32-78).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Sequence
+
+import torch
+
+from .manager import CacheManager
+
+_STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
+
+
+class CacheStorage:
+    def __init__(self, manager: CacheManager, kv_dtype: torch.dtype, device):
+        self.manager = manager
+        self.device = torch.device(device)
+        self.kv_dtype = kv_dtype
+        self.paged: List[torch.Tensor] = []
+        for g in manager.paged_groups:
+            pages = g.pool.first_page + g.pool.num_pages
+            self.paged.append(torch.zeros(
+                (len(g.stops), 2, pages, g.need.num_kv_heads, manager.page_size, g.need.head_dim),
+                dtype=kv_dtype, device=self.device))
+        self.state: List[torch.Tensor] = []
+        for g in manager.state_groups:
+            self.state.append(torch.zeros(
+                (len(g.stops), manager.max_slots + 1) + tuple(g.need.shape),
+                dtype=_STATE_DTYPES[g.need.dtype], device=self.device))
+
+    def kv_of_stop(self, stop: int) -> torch.Tensor:
+        """``[2, pages, kv_heads, page_size, head_dim]`` of one cache-owning stop."""
+        g, i = self.manager.paged_index[stop]
+        return self.paged[g][i]
+
+    def state_of_stop(self, stop: int) -> torch.Tensor:
+        """``[slots + 1, *shape]`` of one cache-owning stop."""
+        g, i = self.manager.state_index[stop]
+        return self.state[g][i]
+
+    def clear_state(self, slots: Sequence[int]) -> None:
+        """Zero the state rows of newly admitted request slots."""
+        if not slots or not self.state:
+            return
+        index = torch.tensor(list(slots), dtype=torch.long, device=self.device)
+        for t in self.state:
+            t.index_fill_(1, index, 0)
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.paged + self.state)
+
+
+def kv_bytes_per_token(manager_needs, kv_dtype: torch.dtype) -> int:
+    """Bytes one token costs over all paged stops (sizing the pool from free
+    memory, cf. python/freetoken/kvcache/mha_pool.py:85-94)."""
+    size = torch.empty((), dtype=kv_dtype).element_size()
+    total = 0
+    for need in manager_needs:
+        if need is not None and need.kind == "paged_kv":
+            total += 2 * need.num_kv_heads * need.head_dim * size
+    return total

@@ -1,0 +1,259 @@
+// Row-wise kernels: embedding gather, residual-add + RMSNorm, fused
+// QK-norm + rotary + KV page store, top-k combine, row gather.
+//
+// All arithmetic is float32 whatever the storage type; one block owns one
+// token, so a token's result does not depend on what else is in the launch.
+//
+// Formulas (reference file:line):
+//   embedding row copy, no scale      python/freetoken/kernel/csrc/jit/index.cu:31-59
+//   z=x+r; r<-z; y=z*rsqrt(mean(z^2)+eps)*w   python/freetoken/kernel/triton/norm.py:101-112
+//   (1+w) form                        python/freetoken/kernel/triton/norm.py:69-72
+//   per-layer QK norm over the whole projection
+//                                     python/freetoken/models/minimax_m2/attention.py:45-47,78-79
+//   per-head QK norm                  python/freetoken/models/minimax_m3/attention.py:54-56,90-91
+//   NeoX / interleaved partial rotary python/freetoken/kernel/triton/rope.py:62-78
+//   K,V rows stored after norm+rotary python/freetoken/kernel/csrc/jit/store.cu:25-53
+//   sum over the k routes in float32  python/freetoken/kernel/triton/fused_moe.py:143-153
+#include "common.cuh"
+
+namespace ft {
+
+// ---------------------------------------------------------------- embedding
+template <typename WT>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
+                                    float* __restrict__ residual, int H, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;  // validated on the host; never index outside the table
+  const WT* row = table + (size_t)id * H;
+  float* out = residual + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_float(row[i]);
+}
+
+// ------------------------------------------------------------------ rmsnorm
+// residual (float32) is updated in place with delta when delta != nullptr.
+template <typename AT>
+__global__ void rmsnorm_kernel(const AT* __restrict__ delta, float* __restrict__ residual,
+                               const float* __restrict__ weight, AT* __restrict__ out, int H,
+                               float eps, int plus_one) {
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  float* r = residual + (size_t)t * H;
+  const AT* d = delta ? delta + (size_t)t * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float z = r[i];
+    if (d) {
+      z += to_float(d[i]);
+      r[i] = z;
+    }
+    ss += z * z;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  AT* o = out + (size_t)t * H;
+  const float one = plus_one ? 1.f : 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    o[i] = from_float<AT>(r[i] * inv * (weight[i] + one));
+  }
+}
+
+// ------------------------------------------------- qk-norm + rotary + store
+struct QkRopeArgs {
+  const void* qkv;        // [T, ld] rows: q (nq*d) | k (nkv*d) | v (nkv*d)
+  void* q_out;            // [T, nq*d]
+  void* kv_pages;         // [2, pages, nkv, P, d]; nullptr: this stop writes no cache
+  const float* q_weight;  // per_layer: [nq*d]; per_head: [d]
+  const float* k_weight;  // per_layer: [nkv*d]; per_head: [d]
+  const float* cos_sin;   // [max_pos, R]: cos (R/2) | sin (R/2); nullptr or R=0: no rotation
+  const int* token_pos;   // [T]
+  const int* token_seg;   // [T]
+  const int* block_table; // [S, table_width]
+  long long ld;
+  long long page_stride;  // elements between pages: nkv*P*d
+  long long kv_stride;    // elements between the K and V halves
+  int nq, nkv, d, R, P, table_width;
+  int norm_mode;          // 0 none, 1 per layer, 2 per head
+  int plus_one, interleaved;
+  float eps;
+};
+
+template <typename AT>
+__global__ void qk_rope_store_kernel(QkRopeArgs a) {
+  extern __shared__ float head_inv[];  // [nq + nkv] for per-head mode
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const AT* row = (const AT*)a.qkv + (size_t)t * a.ld;
+  const int qn = a.nq * a.d, kn = a.nkv * a.d;
+  const AT* q = row;
+  const AT* k = row + qn;
+  const AT* v = row + qn + kn;
+  float inv_q = 1.f, inv_k = 1.f;
+  if (a.norm_mode == 1) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < qn; i += blockDim.x) { float x = to_float(q[i]); s += x * x; }
+    inv_q = rsqrtf(block_sum(s, scratch) / (float)qn + a.eps);
+    s = 0.f;
+    for (int i = threadIdx.x; i < kn; i += blockDim.x) { float x = to_float(k[i]); s += x * x; }
+    inv_k = rsqrtf(block_sum(s, scratch) / (float)kn + a.eps);
+  } else if (a.norm_mode == 2) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int h = warp; h < a.nq + a.nkv; h += nwarps) {
+      const AT* hp = row + (size_t)h * a.d;  // q heads then k heads are contiguous
+      float s = 0.f;
+      for (int i = lane; i < a.d; i += 32) { float x = to_float(hp[i]); s += x * x; }
+      s = warp_sum(s);
+      if (lane == 0) head_inv[h] = rsqrtf(s / (float)a.d + a.eps);
+    }
+    __syncthreads();
+  }
+  const int pos = a.token_pos[t];
+  const int half = a.R >> 1;
+  const float* cs = (a.cos_sin && a.R > 0) ? a.cos_sin + (size_t)pos * a.R : nullptr;
+  const float one = a.plus_one ? 1.f : 0.f;
+
+  AT* qo = (AT*)a.q_out + (size_t)t * qn;
+  AT* ko = nullptr;
+  AT* vo = nullptr;
+  if (a.kv_pages) {
+    const int seg = a.token_seg[t];
+    const int page = a.block_table[(size_t)seg * a.table_width + pos / a.P];
+    const size_t base = (size_t)page * a.page_stride + (size_t)(pos % a.P) * a.d;
+    ko = (AT*)a.kv_pages + base;
+    vo = (AT*)a.kv_pages + a.kv_stride + base;
+  }
+  const size_t head_stride_cache = (size_t)a.P * a.d;
+
+  // One work item = (head, i) for i < d - half: items with i < half rotate the
+  // pair (i, i+half) [NeoX] or (2i, 2i+1) [interleaved]; the others pass one
+  // element beyond the rotary span through.
+  const int per_head = a.d - half;
+  const int total_q = a.nq * per_head, total_k = a.nkv * per_head;
+  for (int w = threadIdx.x; w < total_q + total_k; w += blockDim.x) {
+    const bool is_q = w < total_q;
+    const int ww = is_q ? w : w - total_q;
+    const int h = ww / per_head, i = ww % per_head;
+    const AT* src = (is_q ? q : k) + (size_t)h * a.d;
+    const float* nw = is_q ? a.q_weight : a.k_weight;
+    float inv = 1.f;
+    if (a.norm_mode == 1) inv = is_q ? inv_q : inv_k;
+    if (a.norm_mode == 2) inv = head_inv[is_q ? h : a.nq + h];
+    AT* dst = is_q ? qo + (size_t)h * a.d : (ko ? ko + (size_t)h * head_stride_cache : nullptr);
+    if (!dst) continue;
+    if (i < half) {
+      const int i0 = a.interleaved ? 2 * i : i;
+      const int i1 = a.interleaved ? 2 * i + 1 : i + half;
+      float x0 = to_float(src[i0]), x1 = to_float(src[i1]);
+      if (a.norm_mode) {
+        const int w0 = a.norm_mode == 1 ? h * a.d + i0 : i0;
+        const int w1 = a.norm_mode == 1 ? h * a.d + i1 : i1;
+        x0 = x0 * inv * (nw[w0] + one);
+        x1 = x1 * inv * (nw[w1] + one);
+      }
+      float y0 = x0, y1 = x1;
+      if (cs) {
+        const float c = cs[i], s = cs[half + i];
+        y0 = x0 * c - x1 * s;
+        y1 = x1 * c + x0 * s;
+      }
+      dst[i0] = from_float<AT>(y0);
+      dst[i1] = from_float<AT>(y1);
+    } else {
+      const int i0 = i + half;  // elements R .. d-1
+      float x0 = to_float(src[i0]);
+      if (a.norm_mode) {
+        const int w0 = a.norm_mode == 1 ? h * a.d + i0 : i0;
+        x0 = x0 * inv * (nw[w0] + one);
+      }
+      dst[i0] = from_float<AT>(x0);
+    }
+  }
+  if (vo) {
+    for (int w = threadIdx.x; w < kn; w += blockDim.x) {
+      const int h = w / a.d, i = w % a.d;
+      vo[(size_t)h * head_stride_cache + i] = v[w];
+    }
+  }
+}
+
+// --------------------------------------------------------------- top-k sum
+// out[t,:] = sum_j parts[t*k+j,:] in float32, j ascending.
+template <typename AT>
+__global__ void combine_kernel(const AT* __restrict__ parts, AT* __restrict__ out, int k, int H) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float s = 0.f;
+    for (int j = 0; j < k; ++j) s += to_float(parts[((size_t)t * k + j) * H + i]);
+    out[(size_t)t * H + i] = from_float<AT>(s);
+  }
+}
+
+// ---------------------------------------------------------------- row gather
+template <typename AT>
+__global__ void gather_rows_kernel(const AT* __restrict__ src, const int* __restrict__ rows,
+                                   AT* __restrict__ dst, int H) {
+  const int r = blockIdx.x;
+  const AT* s = src + (size_t)rows[r] * H;
+  AT* d = dst + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) d[i] = s[i];
+}
+
+}  // namespace ft
+
+using namespace ft;
+
+extern "C" {
+
+int ft_embed_gather(const int* ids, const void* table, int table_dtype, float* residual, int T,
+                    int H, int vocab, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  FT_DISPATCH(table_dtype, WT,
+              embed_gather_kernel<WT><<<T, 256, 0, stream>>>(ids, (const WT*)table, residual, H, vocab));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_rmsnorm(const void* delta, float* residual, const float* weight, void* out, int dtype,
+               int T, int H, float eps, int plus_one, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  FT_DISPATCH(dtype, AT,
+              rmsnorm_kernel<AT><<<T, 256, 0, stream>>>((const AT*)delta, residual, weight,
+                                                        (AT*)out, H, eps, plus_one));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_qk_rope_store(const void* qkv, void* q_out, void* kv_pages, const float* q_weight,
+                     const float* k_weight, const float* cos_sin, const int* token_pos,
+                     const int* token_seg, const int* block_table, long long ld,
+                     long long page_stride, long long kv_stride, int nq, int nkv, int d, int R,
+                     int P, int table_width, int norm_mode, int plus_one, int interleaved,
+                     float eps, int dtype, int T, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  if (R < 0 || R > d || (R & 1) || norm_mode < 0 || norm_mode > 2) return FT_ERR_SHAPE;
+  QkRopeArgs a{qkv, q_out, kv_pages, q_weight, k_weight, cos_sin, token_pos, token_seg,
+               block_table, ld, page_stride, kv_stride, nq, nkv, d, R, P, table_width,
+               norm_mode, plus_one, interleaved, eps};
+  const size_t smem = (size_t)(nq + nkv) * sizeof(float);
+  FT_DISPATCH(dtype, AT, qk_rope_store_kernel<AT><<<T, 256, smem, stream>>>(a));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_combine(const void* parts, void* out, int dtype, int T, int k, int H, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  FT_DISPATCH(dtype, AT, combine_kernel<AT><<<T, 256, 0, stream>>>((const AT*)parts, (AT*)out, k, H));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_gather_rows(const void* src, const int* rows, void* dst, int dtype, int n, int H,
+                   cudaStream_t stream) {
+  if (n <= 0) return FT_OK;
+  FT_DISPATCH(dtype, AT,
+              gather_rows_kernel<AT><<<n, 256, 0, stream>>>((const AT*)src, rows, (AT*)dst, H));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,158 @@
+// Router scoring / top-k, and the deterministic sort of routes by expert.
+//
+// Router (python/freetoken/models/minimax_m3/moe.py:71-81, softmax variant
+// python/freetoken/moe/fused.py:27-31), all float32:
+//   s = sigmoid(logits) | softmax(logits);  c = s + bias (bias only chooses)
+//   ids = top-k of c (ties: lower expert id);  w = s[ids]
+//   renormalise: w /= (sum w + 1e-20);  w *= scale
+// Sorting: the reference pads and scatters with atomics, so the order inside an
+// expert varies from run to run (python/freetoken/kernel/triton/moe_align.py:18-20).
+// Here one warp per expert scans the routes in order: rows of an expert keep
+// ascending (token, slot) order, run after run.
+#include "common.cuh"
+
+namespace ft {
+
+template <int WARPS>
+__global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                     int* __restrict__ ids, float* __restrict__ weights, int T, int E,
+                                     int k, int softmax_scoring, int renormalize, float scale) {
+  extern __shared__ float smem[];  // [WARPS][2][E]: scores, choice values
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * WARPS + warp;
+  if (t >= T) return;
+  float* score = smem + (size_t)warp * 2 * E;
+  float* choice = score + E;
+  const float* x = logits + (size_t)t * E;
+  if (softmax_scoring) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, x[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float p = expf(x[e] - mx);
+      score[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) score[e] = score[e] / sum;
+  } else {
+    for (int e = lane; e < E; e += 32) score[e] = 1.f / (1.f + expf(-x[e]));
+  }
+  for (int e = lane; e < E; e += 32) choice[e] = score[e] + (bias ? bias[e] : 0.f);
+  __syncwarp();
+  float wsum = 0.f;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float c = choice[e];
+      if (c > best) { best = c; arg = e; }  // ascending e: first maximum kept
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (arg == 0x7fffffff) arg = 0;  // all values NaN or -inf: stay in range
+    const float w = score[arg];
+    wsum += w;
+    if (lane == 0) {
+      ids[(size_t)t * k + j] = arg;
+      weights[(size_t)t * k + j] = w;
+      choice[arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    for (int j = 0; j < k; ++j) {
+      float w = weights[(size_t)t * k + j];
+      if (renormalize) w = w / (wsum + 1e-20f);
+      weights[(size_t)t * k + j] = w * scale;
+    }
+  }
+}
+
+// counts[e] = number of routes that chose expert e.  One warp per expert.
+__global__ void moe_count_kernel(const int* __restrict__ ids, int* __restrict__ counts, int R, int E) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= E) return;
+  int c = 0;
+  for (int base = 0; base < R; base += 32) {
+    const int r = base + lane;
+    const bool hit = r < R && ids[r] == e;
+    c += __popc(__ballot_sync(0xffffffffu, hit));
+  }
+  if (lane == 0) counts[e] = c;
+}
+
+// offsets[e] = sum counts[<e]; sorted_route[offsets[e] + i] = i-th route of
+// expert e in ascending route order; sorted_token = sorted_route / k.
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ counts,
+                                   int* __restrict__ offsets, int* __restrict__ sorted_route,
+                                   int* __restrict__ sorted_token, int R, int E, int k) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= E) return;
+  int before = 0;
+  for (int base = 0; base < e; base += 32) {
+    const int i = base + lane;
+    before += i < e ? counts[i] : 0;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+  if (lane == 0) {
+    offsets[e] = before;
+    if (e == E - 1) offsets[E] = before + counts[e];
+  }
+  int at = before;
+  for (int base = 0; base < R; base += 32) {
+    const int r = base + lane;
+    const bool hit = r < R && ids[r] == e;
+    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+    if (hit) {
+      const int dst = at + __popc(ballot & ((1u << lane) - 1u));
+      sorted_route[dst] = r;
+      sorted_token[dst] = r / k;
+    }
+    at += __popc(ballot);
+  }
+}
+
+}  // namespace ft
+
+using namespace ft;
+
+extern "C" {
+
+int ft_router_select(const float* logits, const float* bias, int* ids, float* weights, int T,
+                     int E, int k, int softmax_scoring, int renormalize, float scale,
+                     cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  if (k <= 0 || k > E) return FT_ERR_SHAPE;
+  constexpr int WARPS = 4;
+  const size_t smem = (size_t)WARPS * 2 * E * sizeof(float);
+  if (smem > 200 * 1024) return FT_ERR_SHAPE;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(router_select_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  router_select_kernel<WARPS><<<(T + WARPS - 1) / WARPS, WARPS * 32, smem, stream>>>(
+      logits, bias, ids, weights, T, E, k, softmax_scoring, renormalize, scale);
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_moe_sort(const int* ids, int* counts, int* offsets, int* sorted_route, int* sorted_token,
+                int R, int E, int k, cudaStream_t stream) {
+  if (R <= 0) return FT_OK;
+  const int warps = 4;
+  const int blocks = (E + warps - 1) / warps;
+  moe_count_kernel<<<blocks, warps * 32, 0, stream>>>(ids, counts, R, E);
+  moe_scatter_kernel<<<blocks, warps * 32, 0, stream>>>(ids, counts, offsets, sorted_route,
+                                                        sorted_token, R, E, k);
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,284 @@
+"""Python faces of the CUDA launchers.
+
+Each function checks what the kernel assumes (device, dtype, contiguity,
+sizes), then calls the ``extern "C"`` launcher on the current CUDA stream.  A
+non-zero return code raises :class:`KernelError`; nothing here computes on the
+CPU or through a library in a kernel's place.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+_C = {"p": ctypes.c_void_p, "i": ctypes.c_int, "q": ctypes.c_longlong, "f": ctypes.c_float}
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or CUDA reported a launch error."""
+
+
+_ERRORS = {-101: "unsupported element type", -102: "unsupported shape or size",
+           -103: "size beyond the kernel's limit"}
+
+
+def code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not supported by the kernels") from None
+
+
+_bound = {}
+
+
+def _fn(lib: str, name: str, sig: str):
+    key = (lib, name)
+    f = _bound.get(key)
+    if f is None:
+        f = getattr(build.load(lib), name)
+        f.argtypes = [_C[c] for c in sig.split()] + [ctypes.c_void_p]
+        f.restype = ctypes.c_int
+        _bound[key] = f
+    return f
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, name: str) -> None:
+    if rc != 0:
+        what = _ERRORS.get(rc, f"CUDA error {rc}")
+        raise KernelError(f"{name}: {what}")
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+# ------------------------------------------------------------------ rows
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[t,:] = float(table[ids[t],:])"""
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    _need(residual, "residual", torch.float32)
+    T, H = residual.shape
+    if table.shape[1] != H or ids.numel() != T:
+        raise KernelError("embed_gather: shapes do not match")
+    f = _fn("elementwise", "ft_embed_gather", "p p i p i i i")
+    _check(f(_ptr(ids), _ptr(table), code(table.dtype), _ptr(residual), T, H, table.shape[0],
+             _stream()), "embed_gather")
+
+
+def rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor,
+            out: torch.Tensor, eps: float, plus_one: bool) -> None:
+    """residual += delta (if given); out = residual * rsqrt(mean(residual^2)+eps) * (weight [+1])"""
+    _need(residual, "residual", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out")
+    T, H = residual.shape
+    if delta is not None:
+        _need(delta, "delta", out.dtype)
+        if delta.shape != residual.shape:
+            raise KernelError("rmsnorm: delta and residual differ in shape")
+    if out.shape != residual.shape or weight.numel() != H:
+        raise KernelError("rmsnorm: shapes do not match")
+    f = _fn("elementwise", "ft_rmsnorm", "p p p p i i i f i")
+    _check(f(_ptr(delta), _ptr(residual), _ptr(weight), _ptr(out), code(out.dtype), T, H,
+             float(eps), int(plus_one), _stream()), "rmsnorm")
+
+
+def qk_rope_store(qkv: torch.Tensor, q_out: torch.Tensor, kv_pages: Optional[torch.Tensor],
+                  q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                  cos_sin: Optional[torch.Tensor], token_pos: torch.Tensor,
+                  token_seg: torch.Tensor, block_table: torch.Tensor, num_heads: int,
+                  num_kv_heads: int, head_dim: int, rotary_dim: int, norm_mode: int,
+                  plus_one: bool, interleaved: bool, eps: float) -> None:
+    """QK norm (0 none, 1 per layer, 2 per head), partial rotary, K/V page store.
+
+    ``kv_pages`` is ``[2, pages, kv_heads, page_size, head_dim]`` or ``None``
+    for a stop that reads another stop's cache."""
+    _need(qkv, "qkv", contiguous=False)
+    _need(q_out, "q_out", qkv.dtype)
+    T = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape[1] != width or qkv.stride(1) != 1:
+        raise KernelError("qk_rope_store: qkv rows must be [q | k | v] with unit stride")
+    for name, t in (("token_pos", token_pos), ("token_seg", token_seg), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    page_stride = kv_stride = 0
+    P = 1
+    if kv_pages is not None:
+        _need(kv_pages, "kv_pages", qkv.dtype)
+        if kv_pages.dim() != 5 or kv_pages.shape[0] != 2 or kv_pages.shape[2] != num_kv_heads \
+                or kv_pages.shape[4] != head_dim:
+            raise KernelError("qk_rope_store: kv_pages must be [2, pages, kv_heads, page, head_dim]")
+        P = kv_pages.shape[3]
+        page_stride, kv_stride = kv_pages.stride(1), kv_pages.stride(0)
+    if norm_mode:
+        want = (num_heads * head_dim, num_kv_heads * head_dim) if norm_mode == 1 else (head_dim, head_dim)
+        _need(q_weight, "q_weight", torch.float32)
+        _need(k_weight, "k_weight", torch.float32)
+        if q_weight.numel() != want[0] or k_weight.numel() != want[1]:
+            raise KernelError("qk_rope_store: norm weights have the wrong length")
+    if rotary_dim:
+        _need(cos_sin, "cos_sin", torch.float32)
+        if cos_sin.shape[1] != rotary_dim:
+            raise KernelError("qk_rope_store: cos_sin table width differs from rotary_dim")
+    f = _fn("elementwise", "ft_qk_rope_store",
+            "p p p p p p p p p q q q i i i i i i i i i f i i")
+    _check(f(_ptr(qkv), _ptr(q_out), _ptr(kv_pages), _ptr(q_weight), _ptr(k_weight),
+             _ptr(cos_sin) if rotary_dim else None, _ptr(token_pos), _ptr(token_seg),
+             _ptr(block_table), qkv.stride(0), page_stride, kv_stride, num_heads, num_kv_heads,
+             head_dim, rotary_dim, P, block_table.shape[1], norm_mode, int(plus_one),
+             int(interleaved), float(eps), code(qkv.dtype), T, _stream()), "qk_rope_store")
+
+
+def combine(parts: torch.Tensor, out: torch.Tensor, k: int) -> None:
+    """out[t,:] = sum_j parts[t*k+j,:] (float32 sum, ascending j)"""
+    _need(parts, "parts")
+    _need(out, "out", parts.dtype)
+    T, H = out.shape
+    if parts.shape[0] != T * k or parts.shape[1] != H:
+        raise KernelError("combine: shapes do not match")
+    f = _fn("elementwise", "ft_combine", "p p i i i i")
+    _check(f(_ptr(parts), _ptr(out), code(out.dtype), T, k, H, _stream()), "combine")
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, dst: torch.Tensor) -> None:
+    _need(src, "src")
+    _need(rows, "rows", torch.int32)
+    _need(dst, "dst", src.dtype)
+    n, H = dst.shape
+    if src.shape[1] != H or rows.numel() != n:
+        raise KernelError("gather_rows: shapes do not match")
+    f = _fn("elementwise", "ft_gather_rows", "p p p i i i")
+    _check(f(_ptr(src), _ptr(rows), _ptr(dst), code(src.dtype), n, H, _stream()), "gather_rows")
+
+
+# ------------------------------------------------------------------ gemm
+def gemm_rows(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
+              group_offsets: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
+              c_rows: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
+              rows: Optional[int] = None, glu: bool = False, act: str = "silu",
+              act_alpha: float = 1.702, act_limit: float = 7.0) -> None:
+    """c = a @ w^T on CUDA cores in float32 (dense, or grouped by expert).
+
+    ``w`` is ``[N_w, K]`` or ``[G, N_w, K]``; with ``glu`` the N outputs are
+    ``act(w[:N] a) * (w[N:] a)``.  ``rows`` is the number of (sorted) rows when
+    ``a_rows`` / ``c_rows`` redirect them."""
+    _need(a, "a", contiguous=False)
+    _need(w, "w")
+    _need(c, "c", contiguous=False)
+    if w.dim() == 2:
+        G, NW, K = 1, w.shape[0], w.shape[1]
+    else:
+        G, NW, K = w.shape
+    N = NW // 2 if glu else NW
+    M = rows if rows is not None else a.shape[0]
+    if a.shape[1] != K or c.shape[1] != N or a.stride(1) != 1 or c.stride(1) != 1:
+        raise KernelError("gemm_rows: shapes do not match")
+    if (G > 1) != (group_offsets is not None):
+        raise KernelError("gemm_rows: group_offsets must be given exactly for grouped weights")
+    for name, t in (("group_offsets", group_offsets), ("a_rows", a_rows), ("c_rows", c_rows)):
+        if t is not None:
+            _need(t, name, torch.int32)
+    if row_scale is not None:
+        _need(row_scale, "row_scale", torch.float32)
+    f = _fn("gemm_simt", "ft_gemm_rows", "p i q p i q p i q p p p p i i i i i i f f")
+    _check(f(_ptr(a), code(a.dtype), a.stride(0), _ptr(w), code(w.dtype), NW * K, _ptr(c),
+             code(c.dtype), c.stride(0), _ptr(group_offsets), _ptr(a_rows), _ptr(c_rows),
+             _ptr(row_scale), M, N, K, G, int(glu), 0 if act == "silu" else 1, float(act_alpha),
+             float(act_limit), _stream()), "gemm_rows")
+
+
+# ------------------------------------------------------------- attention
+def attn_paged_simt(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
+                    token_pos: torch.Tensor, token_seg: torch.Tensor, block_table: torch.Tensor,
+                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                    window: Optional[int]) -> None:
+    _need(q, "q")
+    _need(out, "out", q.dtype)
+    _need(kv_pages, "kv_pages", q.dtype)
+    for name, t in (("token_pos", token_pos), ("token_seg", token_seg), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    T = q.shape[0]
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+        raise KernelError("attn_paged_simt: q/out must be [T, heads*head_dim]")
+    f = _fn("attention_simt", "ft_attn_paged_simt", "p p p p p p q q i i i i i i f i i")
+    _check(f(_ptr(q), _ptr(out), _ptr(kv_pages), _ptr(token_pos), _ptr(token_seg),
+             _ptr(block_table), kv_pages.stride(1), kv_pages.stride(0), num_heads, num_kv_heads,
+             head_dim, kv_pages.shape[3], block_table.shape[1], int(window or 0), float(scale),
+             code(q.dtype), T, _stream()), "attn_paged_simt")
+
+
+# ---------------------------------------------------------------- router
+def router_select(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
+                  weights: torch.Tensor, k: int, softmax_scoring: bool, renormalize: bool,
+                  scale: float) -> None:
+    _need(logits, "logits", torch.float32)
+    _need(ids, "ids", torch.int32)
+    _need(weights, "weights", torch.float32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    T, E = logits.shape
+    f = _fn("moe_route", "ft_router_select", "p p p p i i i i i f")
+    _check(f(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(weights), T, E, k, int(softmax_scoring),
+             int(renormalize), float(scale), _stream()), "router_select")
+
+
+def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor,
+             sorted_route: torch.Tensor, sorted_token: torch.Tensor, num_experts: int,
+             k: int) -> None:
+    """Stable counting sort of the ``T*k`` routes by expert."""
+    for name, t in (("ids", ids), ("counts", counts), ("offsets", offsets),
+                    ("sorted_route", sorted_route), ("sorted_token", sorted_token)):
+        _need(t, name, torch.int32)
+    R = ids.numel()
+    if counts.numel() < num_experts or offsets.numel() < num_experts + 1 \
+            or sorted_route.numel() < R or sorted_token.numel() < R:
+        raise KernelError("moe_sort: output buffers are too small")
+    f = _fn("moe_route", "ft_moe_sort", "p p p p p i i i")
+    _check(f(_ptr(ids), _ptr(counts), _ptr(offsets), _ptr(sorted_route), _ptr(sorted_token), R,
+             num_experts, k, _stream()), "moe_sort")
+
+
+# -------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Optional[torch.Tensor],
+           top_p: Optional[torch.Tensor], uniform: Optional[torch.Tensor], out: torch.Tensor,
+           probs: Optional[torch.Tensor]) -> None:
+    """Per row: argmax when its temperature <= 0 (or none given), else a
+    temperature / top-k / top-p inverse-CDF draw with the row's uniform."""
+    _need(logits, "logits", torch.float32)
+    _need(out, "out", torch.int32)
+    rows, V = logits.shape
+    if temperature is not None:
+        _need(temperature, "temperature", torch.float32)
+        _need(uniform, "uniform", torch.float32)
+        _need(probs, "probs", torch.float32)
+        if probs.numel() < rows * V:
+            raise KernelError("sample: probs scratch is too small")
+    if top_k is not None:
+        _need(top_k, "top_k", torch.int32)
+    if top_p is not None:
+        _need(top_p, "top_p", torch.float32)
+    f = _fn("sampling", "ft_sample", "p p p p p p p i i")
+    _check(f(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform), _ptr(out),
+             _ptr(probs), rows, V, _stream()), "sample")

@@ -1,0 +1,104 @@
+"""The generic decoder: parts built from a plan, run in the plan's order.
+
+``embed -> for stop in schedule: block(stop.layer) -> final norm -> head`` with
+the ``(delta, residual)`` pair carried between blocks
+(python/freetoken/models/minimax_m2/model.py:48-52,66-68).  The model owns no
+sizes and no cache: parts carry their parameters, the engine hands each stop
+its :class:`CacheView`.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheNeed
+from ..config.model_plan import ModelPlan, PartSpec
+from ..csrc import ops
+from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Block, CacheView,
+                          StepContext)
+from ..weights.spec import TensorSpec
+
+
+def _prefix(spec: PartSpec, default: str) -> str:
+    return spec.params.get("prefix", default)
+
+
+class Model:
+    def __init__(self, plan: ModelPlan):
+        plan.validate()
+        self.plan = plan
+        self.embedding = EMBEDDINGS.get(plan.embedding.kind)(plan.embedding, _prefix(plan.embedding, ""))
+        self.blocks: List[Block] = []
+        for layer in plan.layers:
+            mixer = MIXERS.get(layer.mixer.kind)(layer.mixer, layer.prefix)
+            ffn = FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward, layer.prefix)
+            n1 = NORMS.get(layer.mixer_norm.kind)(layer.mixer_norm, layer.prefix)
+            n2 = NORMS.get(layer.feed_forward_norm.kind)(layer.feed_forward_norm, layer.prefix)
+            self.blocks.append(BLOCKS.get(layer.block.kind)(layer.block, layer.prefix, mixer, ffn, n1, n2))
+        self.final_norm = NORMS.get(plan.final_norm.kind)(plan.final_norm, _prefix(plan.final_norm, ""))
+        self.head = HEADS.get(plan.head.kind)(plan.head, _prefix(plan.head, ""))
+
+    # ---- weights ---------------------------------------------------------
+    def parts(self):
+        return [self.embedding, *self.blocks, self.final_norm, self.head]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs: List[TensorSpec] = []
+        seen = set()
+        for part in self.parts():
+            for s in part.tensor_specs():
+                if s.name in seen:
+                    raise ValueError(f"two parts claim the tensor '{s.name}'")
+                seen.add(s.name)
+                specs.append(s)
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype) -> None:
+        for part in self.parts():
+            part.bind(tensors, dtype)
+
+    def libraries(self, dtype: torch.dtype) -> List[str]:
+        names: List[str] = []
+        for part in self.parts():
+            for lib in part.libraries(dtype):
+                if lib not in names:
+                    names.append(lib)
+        return names
+
+    # ---- cache -------------------------------------------------------------
+    def cache_needs(self) -> List[Optional[CacheNeed]]:
+        """Per stop of the schedule: what the cache manager keeps for it
+        (``None`` for stops that keep nothing or read another stop's cache)."""
+        needs: List[Optional[CacheNeed]] = []
+        for stop in self.plan.schedule:
+            need = self.blocks[stop.layer].mixer.cache_need() if stop.owns_cache else None
+            needs.append(need)
+        return needs
+
+    # ---- forward ------------------------------------------------------------
+    def forward(self, ctx: StepContext, caches: Sequence[CacheView],
+                logit_rows: torch.Tensor, logits: torch.Tensor,
+                all_rows_in_order: bool = False) -> torch.Tensor:
+        """Run the step's tokens; write float32 logits of ``logit_rows`` into
+        ``logits`` ``[len(logit_rows), vocab]``.  ``all_rows_in_order`` says
+        that ``logit_rows`` is ``0..T-1``, which saves the row gather."""
+        T = ctx.num_tokens
+        H = self.plan.hidden_size
+        residual = ctx.workspace.get("model.residual", (T, H), torch.float32)
+        self.embedding.forward(ctx, residual)
+        delta = None
+        for stop, cache in zip(self.plan.schedule, caches):
+            delta = self.blocks[stop.layer].forward(ctx, delta, residual, cache)
+        n = logit_rows.numel()
+        if n == 0:
+            # caches are written; nobody asked for logits
+            return logits
+        x = self.final_norm.forward(ctx, delta, residual)
+        if not all_rows_in_order:
+            picked = ctx.workspace.get("model.picked", (n, H), ctx.dtype)
+            ops.gather_rows(x, logit_rows, picked)
+            x = picked
+        self.head.forward(ctx, x, logits)
+        return logits

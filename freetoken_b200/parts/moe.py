@@ -1,0 +1,120 @@
+"""Top-k routed gated-linear-unit experts.
+
+Router, all float32 (python/freetoken/models/minimax_m3/moe.py:71-81;
+softmax variant python/freetoken/moe/fused.py:27-31):
+``logits = x @ Wg^T``; ``s = sigmoid(logits)`` or ``softmax(logits)``;
+experts are chosen by ``s + bias`` (the bias only chooses), weights are the
+unbiased ``s`` of the chosen, optionally renormalised to sum 1, times ``scale``.
+
+Experts (python/freetoken/moe/fused.py:267-337,
+python/freetoken/layers/moe.py:83-92): routes are sorted by expert;
+``m = act(Wgate_e x) * (Wup_e x)`` from one product against ``[gate; up]``;
+``y_route = w_route * (Wdown_e m)`` with the weight applied to the float32
+accumulator; ``y = sum over the k routes`` in float32, slot order.
+Activation ``silu`` or ``swigluoai``
+(python/freetoken/kernel/triton/activation.py:96-107).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..csrc import ops
+from ..weights.spec import Cat, Init, Name, Stack, TensorSpec
+from .base import FeedForward, StepContext, register_feed_forward
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """params: ``hidden_size, intermediate_size, num_experts, top_k, scoring``
+    (sigmoid | softmax), ``use_bias, renormalize, scale, activation`` (silu |
+    swigluoai), ``act_alpha, act_limit, scope`` and ``checkpoint_names``
+    (router, bias, gate_up, down: model-side names below the scope; gate, up,
+    down_each: per-expert checkpoint names with ``{e}``)."""
+
+    def __init__(self, spec, prefix):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        self.E = int(p["num_experts"])
+        self.k = int(p["top_k"])
+        self.softmax = p.get("scoring", "sigmoid") == "softmax"
+        self.use_bias = bool(p.get("use_bias", False))
+        self.renorm = bool(p.get("renormalize", True))
+        self.scale = float(p.get("scale", 1.0))
+        self.act = p.get("activation", "silu")
+        self.act_alpha = float(p.get("act_alpha", 1.702))
+        self.act_limit = float(p.get("act_limit", 7.0))
+        if self.k > self.E:
+            raise ValueError(f"top_k {self.k} exceeds num_experts {self.E}")
+        names = p["checkpoint_names"]
+        self.scope = self.name(p["scope"])
+        self.n_router = f"{self.scope}.{names['router']}"
+        self.n_bias = f"{self.scope}.{names['bias']}"
+        self.n_gate_up = f"{self.scope}.{names['gate_up']}"
+        self.n_down = f"{self.scope}.{names['down']}"
+        self._each = {key: f"{self.scope}.{names[key]}" for key in ("gate", "up", "down_each")}
+        self.w_router = self.w_bias = self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        E, I, H = self.E, self.inter, self.hidden
+        gate_up = Stack(tuple(
+            Cat((Name(self._each["gate"].format(e=e), (I, H)),
+                 Name(self._each["up"].format(e=e), (I, H))), 0) for e in range(E)))
+        down = Stack(tuple(Name(self._each["down_each"].format(e=e), (H, I)) for e in range(E)))
+        return [
+            TensorSpec(self.n_router, (E, H), role="small32", keep_float32_in_file=True),
+            TensorSpec(self.n_bias, (E,), role="small32", keep_float32_in_file=True,
+                       init=Init(0.0, 0.01 if self.use_bias else 0.0), tag="router_bias",
+                       optional=not self.use_bias),
+            TensorSpec(self.n_gate_up, (E, 2 * I, H), sources=(gate_up,)),
+            TensorSpec(self.n_down, (E, H, I), sources=(down,)),
+        ]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype) -> None:
+        self.w_router = tensors[self.n_router]
+        self.w_bias = tensors.get(self.n_bias) if self.use_bias else None
+        self.w_gate_up = tensors[self.n_gate_up]
+        self.w_down = tensors[self.n_down]
+
+    def libraries(self, dtype) -> List[str]:
+        return ["gemm_simt", "moe_route", "elementwise"]
+
+    # ---- forward ----------------------------------------------------------------
+    def route(self, ctx: StepContext, x: torch.Tensor):
+        """``(ids [T,k] int32, weights [T,k] float32)``."""
+        T = x.shape[0]
+        ws = ctx.workspace
+        logits = ws.get("moe.logits", (T, self.E), torch.float32)
+        ops.gemm_rows(x, self.w_router, logits)
+        ids = ws.get("moe.ids", (T, self.k), torch.int32)
+        weights = ws.get("moe.weights", (T, self.k), torch.float32)
+        ops.router_select(logits, self.w_bias, ids, weights, self.k, self.softmax, self.renorm,
+                          self.scale)
+        return ids, weights
+
+    def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
+        T = x.shape[0]
+        R = T * self.k
+        ws = ctx.workspace
+        ids, weights = self.route(ctx, x)
+        counts = ws.get("moe.counts", (self.E,), torch.int32)
+        offsets = ws.get("moe.offsets", (self.E + 1,), torch.int32)
+        sorted_route = ws.get("moe.sorted_route", (R,), torch.int32)
+        sorted_token = ws.get("moe.sorted_token", (R,), torch.int32)
+        ops.moe_sort(ids.view(-1), counts, offsets, sorted_route, sorted_token, self.E, self.k)
+        mid = ws.get("moe.mid", (R, self.inter), ctx.dtype)
+        parts = ws.get("moe.parts", (R, self.hidden), ctx.dtype)
+        self.experts(ctx, x, mid, parts, offsets, sorted_route, sorted_token, weights.view(-1), R)
+        out = ws.get("moe.out", (T, self.hidden), ctx.dtype)
+        ops.combine(parts, out, self.k)
+        return out
+
+    def experts(self, ctx, x, mid, parts, offsets, sorted_route, sorted_token, route_weight, R):
+        ops.gemm_rows(x, self.w_gate_up, mid, group_offsets=offsets, a_rows=sorted_token, rows=R,
+                      glu=True, act=self.act, act_alpha=self.act_alpha, act_limit=self.act_limit)
+        ops.gemm_rows(mid, self.w_down, parts, group_offsets=offsets, c_rows=sorted_route,
+                      row_scale=route_weight, rows=R)

@@ -1,0 +1,109 @@
+"""The engine against the plain implementation: whole, decoded tail, portions,
+mixed batches with page reuse; in float32 and bfloat16; two (three) tiny
+configurations that differ in every size and option."""
+
+import os
+
+import pytest
+import torch
+
+import replay_driver as rd
+import tiny
+from plain_model import PlainModel
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 9, 17, 70], "B": [1, 6, 13, 31, 80], "C": [3, 40, 66, 90, 21]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for which in tiny.TINY:
+        folder = str(tmp_path_factory.mktemp(f"tiny{which}"))
+        tiny.write_tiny(folder, which)
+        out[which] = folder
+    return out
+
+
+@pytest.fixture(scope="module")
+def expected(models):
+    """Whole-sequence logits of the plain implementation, per model, dtype, request."""
+    cache = {}
+
+    def get(which, dtype):
+        key = (which, dtype)
+        if key not in cache:
+            plain = PlainModel(models[which], dtype)
+            cache[key] = {rid: plain.forward(toks) for rid, toks in requests_of(which).items()}
+        return cache[key]
+    return get
+
+
+def requests_of(which):
+    vocab = tiny.TINY[which]["vocab_size"]
+    return {f"r{i}": tiny.tokens(100 * i + len(which), n, vocab) for i, n in enumerate(LENGTHS[which])}
+
+
+def make_engine(folder, dtype, page, max_tokens, live=4):
+    from freetoken_b200.engine import Engine, EngineArgs
+    return Engine.from_folder(folder, EngineArgs(dtype=dtype, page_size=page,
+                                                 num_pages=-(-max_tokens // page),
+                                                 max_running_requests=live))
+
+
+def compare(got, want, dtype, what):
+    for rid in want:
+        g, w = got[rid], want[rid]
+        assert not torch.isnan(g).any(), f"{what}: request {rid} has positions without logits"
+        bad = ~torch.isclose(g, w, **tiny.TOL[dtype])
+        if bad.any():
+            pos = int(bad.any(dim=1).nonzero()[0])
+            err = (g - w).abs().max().item()
+            raise AssertionError(
+                f"{what} [{dtype}] request {rid}: first wrong position {pos} of {len(w)}, "
+                f"max abs error {err:.3e}")
+
+
+CUTS = {"whole": rd.whole, "decode_tail": rd.decode_tail, "portions": rd.portions, "mixed": rd.mixed}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+@pytest.mark.parametrize("cut", list(CUTS))
+def test_cut_matches_plain(models, expected, which, dtype, cut):
+    reqs = requests_of(which)
+    schedule = CUTS[cut](reqs)
+    page = tiny.PAGE[which]
+    # exactly as many pages as the schedule's peak needs: pages are reused
+    engine = make_engine(models[which], dtype, page, rd.peak_tokens(schedule, page))
+    got = rd.run_engine(engine, reqs, schedule)
+    compare(got, expected(which, dtype), dtype, cut)
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_float32_cuts_agree_bitwise(models, which):
+    """In float32 the logits at a position do not depend on the cut at all."""
+    reqs = requests_of(which)
+    page = tiny.PAGE[which]
+    results = {}
+    for cut, fn in CUTS.items():
+        schedule = fn(reqs)
+        engine = make_engine(models[which], "float32", page, rd.peak_tokens(schedule, page))
+        results[cut] = rd.run_engine(engine, reqs, schedule)
+    for cut in ("decode_tail", "portions", "mixed"):
+        for rid in reqs:
+            assert torch.equal(results[cut][rid], results["whole"][rid]), (cut, rid)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_tool(models, expected, tmp_path, dtype):
+    """bin/trace_run as a child process: mixed schedule, scarce pages."""
+    which = "B"
+    reqs = requests_of(which)
+    schedule = rd.mixed(reqs)
+    page = 16
+    got = rd.run_trace_tool(models[which], dtype, reqs, schedule, str(tmp_path / "out"),
+                            rd.peak_tokens(schedule, page), page, tiny.TINY[which]["vocab_size"])
+    compare(got, expected(which, dtype), dtype, "trace_run mixed")
