@@ -38,6 +38,20 @@ def code(dtype: torch.dtype) -> int:
 
 _bound = {}
 
+# How many of this package's kernels were launched since the counter was last
+# reset; a launcher that starts two kernels counts as two.
+LAUNCHES = 0
+_KERNELS_PER_CALL = {"ft_moe_sort": 2}
+
+
+def reset_launch_count() -> None:
+    global LAUNCHES
+    LAUNCHES = 0
+
+
+def launch_count() -> int:
+    return LAUNCHES
+
 
 def _fn(lib: str, name: str, sig: str):
     key = (lib, name)
@@ -59,6 +73,8 @@ def _stream() -> int:
 
 
 def _check(rc: int, name: str) -> None:
+    global LAUNCHES
+    LAUNCHES += _KERNELS_PER_CALL.get("ft_" + name, 1)
     if rc != 0:
         what = _ERRORS.get(rc, f"CUDA error {rc}")
         raise KernelError(f"{name}: {what}")

@@ -261,6 +261,7 @@ class Engine:
         if N:
             h[off["logit_rows"]: off["logit_rows"] + N] = np.asarray(rows, dtype=np.int32)
         dev = self._meta_dev
+        self._last_meta_ints = cur
         dev[:cur].copy_(host[:cur], non_blocking=True)
         self._pinned_events[self._turn_used].record()
 
@@ -278,13 +279,15 @@ class Engine:
         in_order = N == T and rows == list(range(T))
         return ctx, sec("logit_rows", N), N, in_order
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], probe: Optional[Dict[str, Any]] = None) -> torch.Tensor:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` on the
         device, in the order of the entries and of their ``want`` lists."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if not entries:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
         ctx, logit_rows, N, in_order = self.prepare(entries)
+        ctx.probe = probe
+        self.last_meta_ints = self._last_meta_ints
         self.storage.clear_state(self.cache.take_fresh_slots())
         logits = self.workspace.get("engine.logits", (N, self.plan.vocab_size), torch.float32)
         self.model.forward(ctx, self.cache_views, logit_rows, logits, in_order)

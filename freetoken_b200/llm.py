@@ -1,0 +1,136 @@
+"""The Python entry point: ``LLM(model_path, dtype, **options).generate(...)``.
+
+In the reference's manner (python/freetoken/llm/llm.py:30-43,105-142):
+``LLM(model_path, dtype=torch.bfloat16, **kwargs)`` with the scheduler's option
+names as keywords (``max_running_req``, ``page_size``, ``num_page_override``,
+``max_extend_tokens``, ``max_seq_len_override``, ``memory_ratio``,
+``use_dummy_weight``; python/freetoken/engine/config.py:16-105,
+python/freetoken/scheduler/config.py:14-43), and
+``generate(prompts, sampling_params) -> [{"text", "token_ids"}, ...]`` where
+prompts are token-id lists or, if the model folder has a tokenizer, strings.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+from typing import Any, Dict, List, Optional, Sequence, Union
+
+import torch
+
+from .engine.engine import Engine, EngineArgs, StepEntry
+from .engine.scheduler import PlannedEntry, Request, Scheduler
+from .sampling.params import SamplingParams
+from .sampling.sampler import RequestRng, Sampler
+
+
+def _eos_ids(folder: Optional[str], config: Dict[str, Any]) -> List[int]:
+    """EOS ids of config.json and generation_config.json
+    (python/freetoken/utils/hf.py:44-72)."""
+    ids: List[int] = []
+
+    def add(value) -> None:
+        if isinstance(value, int):
+            ids.append(value)
+        elif isinstance(value, (list, tuple)):
+            ids.extend(int(v) for v in value)
+
+    add(config.get("eos_token_id"))
+    add((config.get("text_config") or {}).get("eos_token_id"))
+    if folder:
+        path = os.path.join(folder, "generation_config.json")
+        if os.path.exists(path):
+            with open(path) as f:
+                add(json.load(f).get("eos_token_id"))
+    return sorted(set(ids))
+
+
+class LLM:
+    def __init__(self, model_path: str, dtype: Union[torch.dtype, str] = torch.bfloat16, *,
+                 max_running_req: int = 4, page_size: int = 64,
+                 num_page_override: Optional[int] = None, num_token_override: Optional[int] = None,
+                 max_extend_tokens: int = 8192, max_seq_len_override: Optional[int] = None,
+                 memory_ratio: float = 0.9, use_dummy_weight: bool = False, seed: int = 0,
+                 device: str = "cuda:0", config: Optional[Dict[str, Any]] = None):
+        """``model_path``: a folder with ``config.json`` and safetensors files.
+        With ``use_dummy_weight`` only ``config.json`` (or ``config``) is
+        needed and weights are random from ``seed``."""
+        args = EngineArgs(dtype=dtype, device=device, page_size=page_size,
+                          num_pages=num_page_override, max_tokens=num_token_override,
+                          max_running_requests=max_running_req, max_seq_len=max_seq_len_override,
+                          memory_ratio=memory_ratio, max_step_tokens=max_extend_tokens)
+        raw: Dict[str, Any]
+        if config is not None:
+            raw = dict(config)
+        else:
+            with open(os.path.join(model_path, "config.json")) as f:
+                raw = json.load(f)
+        if use_dummy_weight:
+            self.engine = Engine.from_config(raw, seed, args)
+        else:
+            self.engine = Engine.from_folder(model_path, args)
+        self.model_path = model_path
+        self.seed = seed
+        self.eos_token_ids = _eos_ids(model_path if config is None else None, raw)
+        self.scheduler = Scheduler(self.engine.cache, max_extend_tokens, self.eos_token_ids)
+        self.sampler = Sampler(self.engine.device, self.engine.vocab_size)
+        self.tokenizer = None
+        self._counter = 0
+
+    # ---- text ------------------------------------------------------------
+    def _tokenizer(self):
+        if self.tokenizer is None:
+            try:
+                from transformers import AutoTokenizer
+                self.tokenizer = AutoTokenizer.from_pretrained(self.model_path)
+            except Exception as exc:  # no tokenizer files, or no tokenizer package
+                raise ValueError(
+                    "text prompts need a tokenizer in the model folder; pass token-id lists instead"
+                ) from exc
+        return self.tokenizer
+
+    # ---- generation ----------------------------------------------------------
+    def generate(self, prompts: Sequence[Union[str, List[int]]],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams]]
+                 ) -> List[Dict[str, Any]]:
+        if isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params] * len(prompts)
+        if len(sampling_params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        requests: List[Request] = []
+        rngs: Dict[Any, RequestRng] = {}
+        for prompt, sp in zip(prompts, sampling_params):
+            ids = self._tokenizer().encode(prompt) if isinstance(prompt, str) else list(prompt)
+            uid = self._counter
+            self._counter += 1
+            r = Request(uid, [int(t) for t in ids], sp)
+            rngs[uid] = RequestRng(sp.seed if sp.seed is not None else self.seed * 1000003 + uid)
+            requests.append(r)
+            self.scheduler.submit(r)
+        while self.scheduler.has_work():
+            self.run_step(rngs)
+        self.scheduler.finished.clear()
+        results = []
+        for r in requests:
+            out = list(r.output)
+            if r.finish_reason == "stop" and out and not r.params.ignore_eos:
+                out = out[:-1]      # the EOS token itself is not part of the answer (llm.py:101-103)
+            text = self.tokenizer.decode(out) if self.tokenizer is not None else ""
+            results.append({"text": text, "token_ids": out, "finish_reason": r.finish_reason})
+        return results
+
+    def run_step(self, rngs: Dict[Any, RequestRng]) -> List[Request]:
+        """Plan one step, run it, sample, record; returns finished requests."""
+        plan = self.scheduler.plan()
+        if not plan:
+            raise RuntimeError("the scheduler has work but could plan nothing: the page pool is too small")
+        entries = [StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.samples else [])
+                   for e in plan]
+        logits = self.engine.step(entries)
+        samplers = [e.request for e in plan if e.samples]
+        sampled: List[int] = []
+        if samplers:
+            params = [r.params for r in samplers]
+            uniforms = [0.0 if r.params.is_greedy else rngs[r.id].next_uniform() for r in samplers]
+            sampled = self.sampler.sample(logits, params, uniforms).cpu().tolist()
+        return self.scheduler.complete(plan, sampled)

@@ -98,6 +98,9 @@ class StepContext:
     max_q_len: int = 1
     max_kv_len: int = 1
     max_positions: int = 0             # longest sequence the engine can hold
+    # when set, parts may leave measurements here (the benchmark counts the
+    # experts a step touched); never set on the serving path
+    probe: Optional[Dict[str, Any]] = None
 
     @property
     def num_segments(self) -> int:
