@@ -39,6 +39,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_simt": "attention_simt.cu",
     "moe_route": "moe_route.cu",
     "sampling": "sampling.cu",
+    "skinny_gemm": "skinny_gemm.cu",
 }
 HEADERS: List[str] = ["common.cuh"]
 EXTRA_LINK: Dict[str, List[str]] = {}

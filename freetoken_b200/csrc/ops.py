@@ -225,6 +225,51 @@ def gemm_rows(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
              float(act_limit), _stream()), "gemm_rows")
 
 
+def skinny_gemm_takes(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool:
+    """Whether the weight-streaming tensor-core kernel takes these operands."""
+    K = w.shape[-1]
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and c.dtype in (torch.bfloat16, torch.float32)
+            and K % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1 and c.stride(1) == 1
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
+
+
+def skinny_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
+                group_offsets: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
+                c_rows: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
+                rows: Optional[int] = None, glu: bool = False, act: str = "silu",
+                act_alpha: float = 1.702, act_limit: float = 7.0, rows_per_pass: int = 8) -> None:
+    """c = a @ w^T for few rows, streaming bfloat16 weights once through
+    mma.sync; same conventions as :func:`gemm_rows`."""
+    _need(a, "a", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    _need(c, "c", contiguous=False)
+    if w.dim() == 2:
+        G, NW, K = 1, w.shape[0], w.shape[1]
+    else:
+        G, NW, K = w.shape
+    N = NW // 2 if glu else NW
+    M = rows if rows is not None else a.shape[0]
+    if a.shape[1] != K or c.shape[1] != N:
+        raise KernelError("skinny_gemm: shapes do not match")
+    if not skinny_gemm_takes(a, w, c):
+        raise KernelError("skinny_gemm: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
+    if (G > 1) != (group_offsets is not None):
+        raise KernelError("skinny_gemm: group_offsets must be given exactly for grouped weights")
+    if rows_per_pass not in (8, 16, 32):
+        raise KernelError("skinny_gemm: rows_per_pass must be 8, 16 or 32")
+    f = _fn("skinny_gemm", "ft_skinny_gemm", "p q p q p i q p p p p i i i i i i f f i")
+    _check(f(_ptr(a), a.stride(0), _ptr(w), NW * K, _ptr(c), code(c.dtype), c.stride(0),
+             _ptr(group_offsets), _ptr(a_rows), _ptr(c_rows), _ptr(row_scale), M, N, K, G,
+             int(glu), 0 if act == "silu" else 1, float(act_alpha), float(act_limit),
+             rows_per_pass, _stream()), "skinny_gemm")
+
+
+def pass_rows(rows: int) -> int:
+    """Tokens per pass of the skinny kernel for ``rows`` rows (per group)."""
+    return 8 if rows <= 8 else (16 if rows <= 16 else 32)
+
+
 # ------------------------------------------------------------- attention
 def attn_paged_simt(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
                     token_pos: torch.Tensor, token_seg: torch.Tensor, block_table: torch.Tensor,

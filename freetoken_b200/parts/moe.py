@@ -81,7 +81,8 @@ class RoutedExperts(FeedForward):
         self.w_down = tensors[self.n_down]
 
     def libraries(self, dtype) -> List[str]:
-        return ["gemm_simt", "moe_route", "elementwise"]
+        libs = ["gemm_simt", "moe_route", "elementwise"]
+        return libs + (["skinny_gemm"] if dtype == torch.bfloat16 else [])
 
     # ---- forward ----------------------------------------------------------------
     def route(self, ctx: StepContext, x: torch.Tensor):
@@ -116,6 +117,15 @@ class RoutedExperts(FeedForward):
         return out
 
     def experts(self, ctx, x, mid, parts, offsets, sorted_route, sorted_token, route_weight, R):
+        if ctx.dtype == torch.bfloat16 and ops.skinny_gemm_takes(x, self.w_gate_up, mid) \
+                and ops.skinny_gemm_takes(mid, self.w_down, parts):
+            per_pass = ops.pass_rows(-(-R // self.E))
+            ops.skinny_gemm(x, self.w_gate_up, mid, group_offsets=offsets, a_rows=sorted_token,
+                            rows=R, glu=True, act=self.act, act_alpha=self.act_alpha,
+                            act_limit=self.act_limit, rows_per_pass=per_pass)
+            ops.skinny_gemm(mid, self.w_down, parts, group_offsets=offsets, c_rows=sorted_route,
+                            row_scale=route_weight, rows=R, rows_per_pass=per_pass)
+            return
         ops.gemm_rows(x, self.w_gate_up, mid, group_offsets=offsets, a_rows=sorted_token, rows=R,
                       glu=True, act=self.act, act_alpha=self.act_alpha, act_limit=self.act_limit)
         ops.gemm_rows(mid, self.w_down, parts, group_offsets=offsets, c_rows=sorted_route,
