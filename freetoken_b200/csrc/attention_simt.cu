@@ -23,6 +23,7 @@ struct AttnArgs {
   const int* token_pos;   // [T]
   const int* token_seg;   // [T]
   const int* block_table; // [S, table_width]
+  const int* rows;        // token rows to process, or nullptr for 0..T-1
   long long page_stride, kv_stride;
   int nq, nkv, d, P, table_width, window;  // window <= 0: none
   float scale;
@@ -32,7 +33,7 @@ template <typename AT, bool EXACT>
 __global__ void __launch_bounds__(128) attn_paged_kernel(AttnArgs a) {
   extern __shared__ float qs[];  // [4 warps][d]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x;
+  const int t = a.rows ? a.rows[blockIdx.x] : blockIdx.x;
   const int h = blockIdx.y * 4 + warp;
   if (h >= a.nq) return;
   const int kvh = h / (a.nq / a.nkv);
@@ -100,13 +101,13 @@ using namespace ft;
 
 extern "C" int ft_attn_paged_simt(const void* q, void* out, const void* kv_pages,
                                   const int* token_pos, const int* token_seg,
-                                  const int* block_table, long long page_stride,
-                                  long long kv_stride, int nq, int nkv, int d, int P,
+                                  const int* block_table, const int* rows,
+                                  long long page_stride, long long kv_stride, int nq, int nkv, int d, int P,
                                   int table_width, int window, float scale, int dtype, int T,
                                   cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if (d > 256 || d <= 0 || nkv <= 0 || nq % nkv) return FT_ERR_SHAPE;
-  AttnArgs a{q, out, kv_pages, token_pos, token_seg, block_table, page_stride, kv_stride,
+  AttnArgs a{q, out, kv_pages, token_pos, token_seg, block_table, rows, page_stride, kv_stride,
              nq, nkv, d, P, table_width, window, scale};
   dim3 grid(T, (nq + 3) / 4);
   const size_t smem = 4 * (size_t)d * sizeof(float);

@@ -40,6 +40,7 @@ LIBRARIES: Dict[str, str] = {
     "moe_route": "moe_route.cu",
     "sampling": "sampling.cu",
     "skinny_gemm": "skinny_gemm.cu",
+    "attention_decode": "attention_decode.cu",
 }
 HEADERS: List[str] = ["common.cuh"]
 EXTRA_LINK: Dict[str, List[str]] = {}

@@ -74,6 +74,27 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   }
 }
 
+// Router logits for few tokens: one warp per expert row.  logits[t,e] =
+// sum_h x[t,h] * W[e,h] in float32; a lane sums its strided share in ascending
+// h, lanes are added by an xor-shuffle tree - the same arithmetic for a token
+// whatever else is in the launch.
+template <typename AT>
+__global__ void router_logits_kernel(const AT* __restrict__ x, long long ldx,
+                                     const float* __restrict__ W, float* __restrict__ logits,
+                                     int T, int E, int H) {
+  const int lane = threadIdx.x & 31;
+  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (e >= E) return;
+  const float* w = W + (size_t)e * H;
+  for (int t = 0; t < T; ++t) {
+    const AT* xr = x + (size_t)t * ldx;
+    float s = 0.f;
+    for (int h = lane; h < H; h += 32) s = fmaf(to_float(xr[h]), w[h], s);
+    s = warp_sum(s);
+    if (lane == 0) logits[(size_t)t * E + e] = s;
+  }
+}
+
 // counts[e] = number of routes that chose expert e.  One warp per expert.
 __global__ void moe_count_kernel(const int* __restrict__ ids, int* __restrict__ counts, int R, int E) {
   const int lane = threadIdx.x & 31;
@@ -139,6 +160,17 @@ int ft_router_select(const float* logits, const float* bias, int* ids, float* we
     cudaFuncSetAttribute(router_select_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   router_select_kernel<WARPS><<<(T + WARPS - 1) / WARPS, WARPS * 32, smem, stream>>>(
       logits, bias, ids, weights, T, E, k, softmax_scoring, renormalize, scale);
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_router_logits(const void* x, int x_dtype, long long ldx, const float* W, float* logits,
+                     int T, int E, int H, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  const int warps = 4;
+  const int blocks = (E + warps - 1) / warps;
+  FT_DISPATCH(x_dtype, AT,
+              router_logits_kernel<AT><<<blocks, warps * 32, 0, stream>>>((const AT*)x, ldx, W, logits, T, E, H));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

@@ -41,7 +41,7 @@ _bound = {}
 # How many of this package's kernels were launched since the counter was last
 # reset; a launcher that starts two kernels counts as two.
 LAUNCHES = 0
-_KERNELS_PER_CALL = {"ft_moe_sort": 2}
+_KERNELS_PER_CALL = {"ft_moe_sort": 2, "ft_attn_decode": 2}
 
 
 def reset_launch_count() -> None:
@@ -274,20 +274,77 @@ def pass_rows(rows: int) -> int:
 def attn_paged_simt(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
                     token_pos: torch.Tensor, token_seg: torch.Tensor, block_table: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                    window: Optional[int]) -> None:
+                    window: Optional[int], rows: Optional[torch.Tensor] = None) -> None:
+    """Generic paged attention; ``rows`` limits it to those token rows."""
     _need(q, "q")
     _need(out, "out", q.dtype)
     _need(kv_pages, "kv_pages", q.dtype)
     for name, t in (("token_pos", token_pos), ("token_seg", token_seg), ("block_table", block_table)):
         _need(t, name, torch.int32)
-    T = q.shape[0]
+    T = q.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
     if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
         raise KernelError("attn_paged_simt: q/out must be [T, heads*head_dim]")
-    f = _fn("attention_simt", "ft_attn_paged_simt", "p p p p p p q q i i i i i i f i i")
+    f = _fn("attention_simt", "ft_attn_paged_simt", "p p p p p p p q q i i i i i i f i i")
     _check(f(_ptr(q), _ptr(out), _ptr(kv_pages), _ptr(token_pos), _ptr(token_seg),
-             _ptr(block_table), kv_pages.stride(1), kv_pages.stride(0), num_heads, num_kv_heads,
+             _ptr(block_table), _ptr(rows), kv_pages.stride(1), kv_pages.stride(0), num_heads, num_kv_heads,
              head_dim, kv_pages.shape[3], block_table.shape[1], int(window or 0), float(scale),
              code(q.dtype), T, _stream()), "attn_paged_simt")
+
+
+DECODE_HEAD_DIMS = (32, 64, 128)
+_SM_COUNT = {}
+
+
+def sm_count(device) -> int:
+    idx = torch.device(device).index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+def attn_decode_takes(q: torch.Tensor, head_dim: int) -> bool:
+    return q.dtype == torch.bfloat16 and head_dim in DECODE_HEAD_DIMS
+
+
+def decode_splits(n_rows: int, num_kv_heads: int, group: int, max_kv_len: int, sms: int):
+    """``(splits, keys per split)``: enough CTAs to fill the SMs twice, whole 64-key tiles."""
+    base = max(1, n_rows * num_kv_heads * (-(-group // 16)))
+    tiles = max(1, -(-max_kv_len // 64))
+    splits = min(max(1, -(-2 * sms // base)), tiles, 64)
+    split_keys = -(-tiles // splits) * 64
+    splits = -(-tiles * 64 // split_keys)
+    return splits, split_keys
+
+
+def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
+                rows: Optional[torch.Tensor], n_rows: int, token_pos: torch.Tensor,
+                token_seg: torch.Tensor, block_table: torch.Tensor, num_heads: int,
+                num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
+                max_kv_len: int, workspace) -> None:
+    """Split-KV tensor-core attention for single-token rows (bfloat16)."""
+    _need(q, "q", torch.bfloat16)
+    _need(out, "out", torch.bfloat16)
+    _need(kv_pages, "kv_pages", torch.bfloat16)
+    if not attn_decode_takes(q, head_dim):
+        raise KernelError(f"attn_decode: head_dim {head_dim} not in {DECODE_HEAD_DIMS}")
+    for name, t in (("token_pos", token_pos), ("token_seg", token_seg), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    splits, split_keys = decode_splits(n_rows, num_kv_heads, num_heads // num_kv_heads, max_kv_len,
+                                       sm_count(q.device))
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = workspace.get("attn.part_o", (n_rows, num_heads, splits, head_dim), torch.float32)
+        part_ml = workspace.get("attn.part_ml", (n_rows, num_heads, splits, 2), torch.float32)
+    f = _fn("attention_decode", "ft_attn_decode", "p p p p p p p p p q q i i i i i i i i i f")
+    _check(f(_ptr(q), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(kv_pages), _ptr(rows),
+             _ptr(token_pos), _ptr(token_seg), _ptr(block_table), kv_pages.stride(1),
+             kv_pages.stride(0), num_heads, num_kv_heads, head_dim, kv_pages.shape[3],
+             block_table.shape[1], int(window or 0), n_rows, splits, split_keys, float(scale),
+             _stream()), "attn_decode")
 
 
 # ---------------------------------------------------------------- router
@@ -303,6 +360,20 @@ def router_select(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch
     f = _fn("moe_route", "ft_router_select", "p p p p i i i i i f")
     _check(f(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(weights), T, E, k, int(softmax_scoring),
              int(renormalize), float(scale), _stream()), "router_select")
+
+
+def router_logits(x: torch.Tensor, w: torch.Tensor, logits: torch.Tensor) -> None:
+    """logits = x @ w^T in float32 for few tokens (one warp per expert row)."""
+    _need(x, "x", contiguous=False)
+    _need(w, "w", torch.float32)
+    _need(logits, "logits", torch.float32)
+    T, H = x.shape
+    E = w.shape[0]
+    if w.shape[1] != H or logits.shape != (T, E) or x.stride(1) != 1:
+        raise KernelError("router_logits: shapes do not match")
+    f = _fn("moe_route", "ft_router_logits", "p i q p p i i i")
+    _check(f(_ptr(x), code(x.dtype), x.stride(0), _ptr(w), _ptr(logits), T, E, H, _stream()),
+           "router_logits")
 
 
 def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor,

@@ -233,9 +233,12 @@ class Engine:
         # packed layout, every section 16-byte aligned
         off = {}
         cur = 0
+        dec_rows = [s.q_start for s in segments if s.n == 1]
+        pre_rows = [r for s in segments if s.n > 1 for r in range(s.q_start, s.q_start + s.n)]
         for name, size in (("token_ids", T), ("token_pos", T), ("token_seg", T), ("seg_slot", S),
                            ("seg_pos0", S), ("seg_q_start", S + 1), ("seg_kv_len", S),
-                           ("logit_rows", N)):
+                           ("logit_rows", N), ("dec_rows", len(dec_rows)),
+                           ("pre_rows", len(pre_rows))):
             off[name] = cur
             cur = _align4(cur + size)
         for g in range(len(groups)):
@@ -260,6 +263,11 @@ class Engine:
         h[off["seg_q_start"] + S] = T
         if N:
             h[off["logit_rows"]: off["logit_rows"] + N] = np.asarray(rows, dtype=np.int32)
+        mixed = bool(dec_rows) and bool(pre_rows)
+        if dec_rows:
+            h[off["dec_rows"]: off["dec_rows"] + len(dec_rows)] = np.asarray(dec_rows, dtype=np.int32)
+        if pre_rows:
+            h[off["pre_rows"]: off["pre_rows"] + len(pre_rows)] = np.asarray(pre_rows, dtype=np.int32)
         dev = self._meta_dev
         self._last_meta_ints = cur
         dev[:cur].copy_(host[:cur], non_blocking=True)
@@ -275,7 +283,11 @@ class Engine:
             seg_q_start=sec("seg_q_start", S + 1), seg_kv_len=sec("seg_kv_len", S),
             block_tables=[sec(f"table{g}", S * width).view(S, width) for g in range(len(groups))],
             workspace=self.workspace, page_size=P, max_q_len=max_q, max_kv_len=max_kv,
-            max_positions=self.max_seq_len)
+            max_positions=self.max_seq_len,
+            decode_rows=sec("dec_rows", len(dec_rows)) if mixed else None,
+            prefill_rows=sec("pre_rows", len(pre_rows)) if mixed else None,
+            num_decode_rows=len(dec_rows), num_prefill_rows=len(pre_rows),
+            max_decode_kv_len=max((s.pos0 + 1 for s in segments if s.n == 1), default=0))
         in_order = N == T and rows == list(range(T))
         return ctx, sec("logit_rows", N), N, in_order
 

@@ -94,7 +94,8 @@ class PagedAttention(Mixer):
             self.w_knorm = tensors[self.n_knorm]
 
     def libraries(self, dtype) -> List[str]:
-        return ["elementwise", "attention_simt"] + linear.libraries(dtype)
+        fast = ["attention_decode"] if dtype == torch.bfloat16 else []
+        return ["elementwise", "attention_simt"] + fast + linear.libraries(dtype)
 
     # ---- forward ----------------------------------------------------------------
     def forward(self, ctx: StepContext, x: torch.Tensor, cache: CacheView) -> torch.Tensor:
@@ -115,5 +116,17 @@ class PagedAttention(Mixer):
         return linear.linear(o, self.w_o, ws.get("attn.y", (T, self.hidden), ctx.dtype))
 
     def attend(self, ctx: StepContext, q, o, cache: CacheView, table) -> None:
+        """Single-token rows go to the split-KV tensor-core kernel, rows of
+        longer segments to the prefill kernel; sizes those refuse (and the
+        float32 path) go to the generic kernel.  ``decode_rows`` /
+        ``prefill_rows`` are only set when a step has both kinds."""
+        rest = None          # rows left for the generic kernel; None = all rows
+        if ctx.num_decode_rows > 0 and ops.attn_decode_takes(q, self.d):
+            ops.attn_decode(q, o, cache.kv_pages, ctx.decode_rows, ctx.num_decode_rows,
+                            ctx.token_pos, ctx.token_seg, table, self.nq, self.nkv, self.d,
+                            self.scale, self.window, ctx.max_decode_kv_len, ctx.workspace)
+            if ctx.num_prefill_rows == 0:
+                return
+            rest = ctx.prefill_rows
         ops.attn_paged_simt(q, o, cache.kv_pages, ctx.token_pos, ctx.token_seg, table,
-                            self.nq, self.nkv, self.d, self.scale, self.window)
+                            self.nq, self.nkv, self.d, self.scale, self.window, rows=rest)

@@ -98,6 +98,13 @@ class StepContext:
     max_q_len: int = 1
     max_kv_len: int = 1
     max_positions: int = 0             # longest sequence the engine can hold
+    # token rows of single-token segments (decode) and of longer segments, as
+    # device int32 tensors; None when the step has none of that kind
+    decode_rows: Optional[torch.Tensor] = None
+    prefill_rows: Optional[torch.Tensor] = None
+    num_decode_rows: int = 0
+    num_prefill_rows: int = 0
+    max_decode_kv_len: int = 0
     # when set, parts may leave measurements here (the benchmark counts the
     # experts a step touched); never set on the serving path
     probe: Optional[Dict[str, Any]] = None

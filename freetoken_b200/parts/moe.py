@@ -26,6 +26,11 @@ from ..weights.spec import Cat, Init, Name, Stack, TensorSpec
 from .base import FeedForward, StepContext, register_feed_forward
 
 
+# Up to this many tokens the router's logits come from the one-warp-per-expert
+# kernel; above it from the tiled float32 product.
+ROUTER_SMALL_T = 64
+
+
 @register_feed_forward("routed_experts")
 class RoutedExperts(FeedForward):
     """params: ``hidden_size, intermediate_size, num_experts, top_k, scoring``
@@ -90,7 +95,10 @@ class RoutedExperts(FeedForward):
         T = x.shape[0]
         ws = ctx.workspace
         logits = ws.get("moe.logits", (T, self.E), torch.float32)
-        ops.gemm_rows(x, self.w_router, logits)
+        if ctx.dtype == torch.bfloat16 and T <= ROUTER_SMALL_T:
+            ops.router_logits(x, self.w_router, logits)
+        else:
+            ops.gemm_rows(x, self.w_router, logits)
         ids = ws.get("moe.ids", (T, self.k), torch.int32)
         weights = ws.get("moe.weights", (T, self.k), torch.float32)
         ops.router_select(logits, self.w_bias, ids, weights, self.k, self.softmax, self.renorm,

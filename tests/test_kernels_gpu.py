@@ -379,3 +379,47 @@ def test_sample(V):
     # all greedy, no scratch
     ops().sample(logits, None, None, None, None, out, None)
     assert out.tolist() == logits.argmax(-1).tolist()
+
+
+# ------------------------------------------------------ decode attention (mma)
+DECODE_CASES = [
+    # nq, nkv, d, P, single-token segments at positions, window, standout (segment, key)
+    (6, 1, 128, 64, [0, 1, 63, 64, 200], None, None),
+    (48, 8, 128, 64, [2047, 100], None, (0, 5)),          # far key among thousands
+    (4, 2, 32, 4, [37, 9], 6, None),                      # window edge inside small pages
+    (12, 2, 64, 16, [700], None, (0, 333)),               # one row: many splits
+    (40, 2, 64, 32, [130, 64], 100, None),                # group of 20: two head tiles
+    (3, 3, 32, 8, [300, 5, 77], None, None),              # group of 1
+]
+
+
+@pytest.mark.parametrize("nq,nkv,d,P,positions,window,standout", DECODE_CASES)
+def test_attn_decode(nq, nkv, d, P, positions, window, standout):
+    from freetoken_b200.parts.base import Workspace
+    o = ops()
+    lens = [(p, 1) for p in positions]
+    q, kv, pos, seg, table = _paged_case("bfloat16", nq, nkv, d, P, lens, window, standout=standout)
+    out = torch.zeros_like(q)
+    scale = d ** -0.5
+    o.attn_decode(q, out, kv, None, len(positions), pos, seg, table, nq, nkv, d, scale, window,
+                  max(positions) + 1, Workspace(DEV))
+    want = _attn_ref(q, kv, pos, seg, table, nq, nkv, d, P, scale, window)
+    assert torch.allclose(out.float().cpu(), want, **TOL["bfloat16"])
+    # a subset of rows through the row list leaves the other rows alone
+    if len(positions) > 1:
+        rows = torch.tensor([len(positions) - 1], dtype=torch.int32, device=DEV)
+        out2 = torch.full_like(q, 7.0)
+        o.attn_decode(q, out2, kv, rows, 1, pos, seg, table, nq, nkv, d, scale, window,
+                      positions[-1] + 1, Workspace(DEV))
+        assert torch.allclose(out2[-1].float().cpu(), want[-1], **TOL["bfloat16"])
+        assert (out2[:-1] == 7.0).all()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,E,H", [(1, 4, 64), (8, 256, 3072), (33, 37, 100)])
+def test_router_logits(dtype, T, E, H):
+    x = rnd(T, H, dtype=DT[dtype], seed=1)
+    w = rnd(E, H, seed=2, scale=0.05)
+    out = torch.empty(T, E, device=DEV)
+    ops().router_logits(x, w, out)
+    assert torch.allclose(out, x.float() @ w.t(), atol=1e-4, rtol=1e-5)
