@@ -116,7 +116,10 @@ class RoutedExperts(FeedForward):
         sorted_token = ws.get("moe.sorted_token", (R,), torch.int32)
         ops.moe_sort(ids.view(-1), counts, offsets, sorted_route, sorted_token, self.E, self.k)
         if ctx.probe is not None:
-            ctx.probe.setdefault("experts_touched", []).append(int((counts > 0).sum()))
+            if "router_ids" in ctx.probe:
+                ctx.probe["router_ids"].append(ids.clone())
+            else:
+                ctx.probe.setdefault("experts_touched", []).append(int((counts > 0).sum()))
         mid = ws.get("moe.mid", (R, self.inter), ctx.dtype)
         parts = ws.get("moe.parts", (R, self.hidden), ctx.dtype)
         self.experts(ctx, x, mid, parts, offsets, sorted_route, sorted_token, weights.view(-1), R)

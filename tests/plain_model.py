@@ -136,12 +136,15 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
 
 
 def route(h: torch.Tensor, gate_w: torch.Tensor, bias: Optional[torch.Tensor], top_k: int,
-          scoring: str, renormalize: bool, scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+          scoring: str, renormalize: bool, scale: float, forced_ids: Optional[torch.Tensor] = None,
+          record: Optional[list] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """logits = h.float() @ Wg.float()^T; s = sigmoid(logits); choose top-k of s + bias;
     weights = s[ids] (unbiased); w /= (sum w + 1e-20); w *= scale.
     python/freetoken/models/minimax_m3/moe.py:71-81.
     softmax variant: s = softmax(logits), top-k of s, python/freetoken/moe/fused.py:27-31.
-    Ties go to the lower expert id (torch.topk leaves the order open)."""
+    Ties go to the lower expert id (torch.topk leaves the order open).
+    ``forced_ids`` replaces the choice (weights still come from this function's
+    own scores); ``record`` receives ``(own ids, margin of the own choice)``."""
     logits = h.float() @ gate_w.float().t()
     s = torch.softmax(logits, dim=-1) if scoring == "softmax" else torch.sigmoid(logits)
     choice = s + (bias.float() if bias is not None else 0.0)
@@ -153,6 +156,13 @@ def route(h: torch.Tensor, gate_w: torch.Tensor, bias: Optional[torch.Tensor], t
         first = (c == best).float().argmax(dim=-1)   # lowest index among equals
         ids[:, j] = first
         c[torch.arange(T), first] = float("-inf")
+    if record is not None:
+        # own choice and its margin: k-th chosen value minus the best value left out
+        kth = choice.gather(-1, ids[:, -1:]).squeeze(-1)
+        left = c.max(dim=-1).values if top_k < E else torch.full((T,), float("-inf"))
+        record.append((ids.clone(), kth - left))
+    if forced_ids is not None:
+        ids = forced_ids.long()
     w = s.gather(-1, ids)
     if renormalize:
         w = w / (w.sum(dim=-1, keepdim=True) + 1e-20)
@@ -222,6 +232,7 @@ class PlainModel:
         self.limit = float(c.get("swiglu_limit", 7.0))
         self.tied = bool(c.get("tie_word_embeddings", False))
         self.window = c.get("sliding_window")
+        self.routing: list = []
 
     def rnd(self, x: torch.Tensor) -> torch.Tensor:
         """Round to the activation dtype of the emulated pipeline."""
@@ -236,7 +247,8 @@ class PlainModel:
             t = t.to(torch.bfloat16)   # matrices are served in bfloat16; the router's stay float32
         return t.float()
 
-    def layer(self, i: int, x: torch.Tensor, residual: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    def layer(self, i: int, x: torch.Tensor, residual: torch.Tensor,
+              forced_ids: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """(x, residual) in -> (x, residual) out; norms do the adds.
         python/freetoken/models/minimax_m2/model.py:27-37."""
         p = f"model.layers.{i}"
@@ -263,22 +275,27 @@ class PlainModel:
         m = f"{p}.block_sparse_moe"
         bias = self.tensors[f"{m}.e_score_correction_bias"] if self.use_bias else None
         wts, ids = route(h2, self.tensors[f"{m}.gate.weight"], bias, self.k, self.scoring,
-                         self.renorm, self.route_scale)
+                         self.renorm, self.route_scale, forced_ids, self.routing)
         gate_up = [torch.cat([self.w(f"{m}.experts.{e}.w1.weight"), self.w(f"{m}.experts.{e}.w3.weight")])
                    for e in range(self.E)]                        # w1 = gate, w3 = up: weight.py:54
         down = [self.w(f"{m}.experts.{e}.w2.weight") for e in range(self.E)]
         y = self.rnd(experts(h2, wts, ids, gate_up, down, self.act, self.alpha, self.limit, self.rnd))
         return y, residual
 
-    def forward(self, tokens: List[int]) -> torch.Tensor:
+    def forward(self, tokens: List[int], forced_routing: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Logits [T, vocab] float32 for the whole sequence.
-        python/freetoken/models/minimax_m2/model.py:48-52,66-68."""
+        python/freetoken/models/minimax_m2/model.py:48-52,66-68.
+        ``forced_routing`` ``[layers, T, k]`` fixes the experts every token
+        uses; ``self.routing`` afterwards holds, per layer, this model's own
+        choice and its margin."""
+        self.routing = []
         ids = torch.tensor(tokens, dtype=torch.long)
         emb = self.w("model.embed_tokens.weight")
         residual = emb[ids]                                        # no scale: embedding.py:39-47
         x = torch.zeros_like(residual)
         for i in range(self.L):
-            x, residual = self.layer(i, x, residual)
+            x, residual = self.layer(i, x, residual,
+                                     None if forced_routing is None else forced_routing[i])
         xf = self.rnd(rms_norm(residual + x, self.w("model.norm.weight"), self.eps, self.plus_one))
         head = emb if self.tied else self.w("lm_head.weight")      # embedding.py:112
         return xf @ head.t()

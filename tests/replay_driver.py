@@ -104,8 +104,11 @@ def peak_tokens(schedule: List[Step], page: int) -> int:
     return peak
 
 
-def run_engine(engine, requests: Dict[str, List[int]], schedule: List[Step]) -> Dict[str, torch.Tensor]:
-    """Drive ``engine.step``; logits of every position of every request."""
+def run_engine(engine, requests: Dict[str, List[int]], schedule: List[Step], routing: Dict = None
+               ) -> Dict[str, torch.Tensor]:
+    """Drive ``engine.step``; logits of every position of every request.  With
+    ``routing`` (a dict) the experts the engine chose are left there as
+    ``routing[request] = int tensor [stops, positions, k]``."""
     from freetoken_b200.engine import StepEntry
 
     V = engine.vocab_size
@@ -113,10 +116,17 @@ def run_engine(engine, requests: Dict[str, List[int]], schedule: List[Step]) -> 
     for entries, ended in schedule:
         batch = [StepEntry(rid, requests[rid][first:first + n], list(range(n)))
                  for rid, first, n in entries]
-        logits = engine.step(batch).float().cpu()
+        probe = {"router_ids": []} if routing is not None else None
+        logits = engine.step(batch, probe=probe).float().cpu()
         row = 0
         for rid, first, n in entries:
             out[rid][first:first + n] = logits[row:row + n]
+            if routing is not None:
+                ids = torch.stack([x[row:row + n].cpu() for x in probe["router_ids"]])   # [stops, n, k]
+                if rid not in routing:
+                    routing[rid] = torch.full((ids.shape[0], len(requests[rid]), ids.shape[2]), -1,
+                                              dtype=torch.int32)
+                routing[rid][:, first:first + n] = ids
             row += n
         for rid in ended:
             engine.end_request(rid)

@@ -52,6 +52,31 @@ def make_engine(folder, dtype, page, max_tokens, live=4):
                                                  max_running_requests=live))
 
 
+# In bfloat16 the discrete choice of experts may differ between two correct
+# implementations where two experts' scores lie within rounding of each other.
+# The bfloat16 comparisons therefore hand the engine's choice to the plain
+# implementation (everything else is still computed by it) and check separately
+# that the two choices differ only where the plain implementation's own margin
+# is small.  float32 comparisons use the plain implementation's own choice.
+MARGIN = 5e-3
+
+
+def plain_logits(models, which, dtype, reqs, routing=None):
+    plain = PlainModel(models[which], dtype)
+    out = {}
+    for rid, toks in reqs.items():
+        forced = None if routing is None else routing[rid]
+        out[rid] = plain.forward(toks, forced)
+        if routing is not None:
+            for layer, (own, margin) in enumerate(plain.routing):
+                differ = (own.sort(-1).values != forced[layer].long().sort(-1).values).any(-1)
+                assert (margin[differ] < MARGIN).all(), (
+                    f"{which} request {rid} layer {layer}: the engine chose other experts at "
+                    f"positions {differ.nonzero().flatten().tolist()} with margins {margin[differ].tolist()}")
+                assert differ.float().mean() <= 0.25, f"too many routing differences in layer {layer}"
+    return out
+
+
 def compare(got, want, dtype, what):
     for rid in want:
         g, w = got[rid], want[rid]
@@ -77,8 +102,14 @@ def test_cut_matches_plain(models, expected, which, dtype, cut):
     page = tiny.PAGE[which]
     # exactly as many pages as the schedule's peak needs: pages are reused
     engine = make_engine(models[which], dtype, page, rd.peak_tokens(schedule, page))
-    got = rd.run_engine(engine, reqs, schedule)
-    compare(got, expected(which, dtype), dtype, cut)
+    if dtype == "float32":
+        got = rd.run_engine(engine, reqs, schedule)
+        want = expected(which, dtype)
+    else:
+        routing = {}
+        got = rd.run_engine(engine, reqs, schedule, routing)
+        want = plain_logits(models, which, dtype, reqs, routing)
+    compare(got, want, dtype, cut)
     assert engine.cache.free_pages() == engine.cache.total_pages()
 
 
@@ -106,4 +137,14 @@ def test_trace_run_tool(models, expected, tmp_path, dtype):
     page = 16
     got = rd.run_trace_tool(models[which], dtype, reqs, schedule, str(tmp_path / "out"),
                             rd.peak_tokens(schedule, page), page, tiny.TINY[which]["vocab_size"])
-    compare(got, expected(which, dtype), dtype, "trace_run mixed")
+    if dtype == "float32":
+        want = expected(which, dtype)
+    else:
+        # the same schedule in this process gives the experts the tool's run chose
+        routing = {}
+        engine = make_engine(models[which], dtype, page, rd.peak_tokens(schedule, page))
+        same = rd.run_engine(engine, reqs, schedule, routing)
+        for rid in reqs:
+            assert torch.equal(same[rid], got[rid]), "the tool and the in-process engine differ"
+        want = plain_logits(models, which, dtype, reqs, routing)
+    compare(got, want, dtype, "trace_run mixed")
