@@ -9,7 +9,7 @@ folder) and ``bench``; option names and meanings are the reference's where it
 has them: ``--model-path/--model``, ``--dtype``, ``--max-running-requests``,
 ``--max-seq-len-override``, ``--memory-ratio``, ``--dummy-weight``,
 ``--max-prefill-length/--max-extend-length``, ``--num-pages`` / ``--num-tokens``,
-``--page-size``; and of ``ft ctl generate``: ``--max-tokens``, ``--ignore-eos``.
+``--page-size``, ``--cuda-graph-max-bs/--graph``; and of ``ft ctl generate``: ``--max-tokens``, ``--ignore-eos``.
 """
 
 from __future__ import annotations
@@ -45,6 +45,8 @@ def _engine_options(p: argparse.ArgumentParser) -> None:
     cap.add_argument("--num-tokens", dest="num_token_override", type=int, default=None,
                      help="KV cache capacity in tokens")
     p.add_argument("--page-size", type=int, default=64, help="tokens per KV cache page")
+    p.add_argument("--cuda-graph-max-bs", "--graph", dest="cuda_graph_max_bs", type=int, default=64,
+                   help="the maximum batch size for CUDA graph capture of decode steps (0: off)")
     p.add_argument("--seed", type=int, default=0, help="seed of random weights and sampling")
 
 
@@ -79,7 +81,8 @@ def _run_generate(argv: Sequence[str]) -> int:
               max_running_req=a.max_running_req, page_size=a.page_size,
               num_page_override=a.num_page_override, num_token_override=a.num_token_override,
               max_extend_tokens=a.max_extend_tokens, max_seq_len_override=a.max_seq_len_override,
-              memory_ratio=a.memory_ratio, use_dummy_weight=a.use_dummy_weight, seed=a.seed)
+              memory_ratio=a.memory_ratio, use_dummy_weight=a.use_dummy_weight,
+              cuda_graph_max_bs=a.cuda_graph_max_bs, seed=a.seed)
     sp = SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
                         ignore_eos=a.ignore_eos, max_tokens=a.max_tokens, seed=a.seed)
     for prompt, result in zip(prompts, llm.generate(prompts, sp)):

@@ -27,7 +27,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage, kv_bytes_per_token
-from ..csrc import build
+from ..csrc import build, ops
 from ..models.model import Model
 from ..parts.base import CacheView, Segment, StepContext, Workspace
 from ..registry import Architecture, architecture_of, get_architecture, read_model_config
@@ -61,6 +61,7 @@ class EngineArgs:
     max_seq_len: Optional[int] = None
     memory_ratio: float = 0.9
     max_step_tokens: int = 8192
+    cuda_graph_max_bs: int = 64              # decode-only steps up to this batch are graph-replayed; 0: never
 
 
 def _align4(n: int) -> int:
@@ -128,6 +129,10 @@ class Engine:
         self._pinned_events: List[torch.cuda.Event] = []
         self._pinned_turn = 0
         self._meta_dev: Optional[torch.Tensor] = None
+        self._meta_generation = 0
+        self._graphs: Dict[Tuple, "torch.cuda.CUDAGraph"] = {}
+        self._graph_seen: Dict[Tuple, int] = {}
+        self.graph_replays = 0
         self.steps = 0
         self.tokens_run = 0
 
@@ -178,6 +183,7 @@ class Engine:
             self._pinned[turn] = torch.empty(max(count, 4096), dtype=torch.int32).pin_memory()
         if self._meta_dev is None or self._meta_dev.numel() < count:
             self._meta_dev = torch.empty(max(count, 4096), dtype=torch.int32, device=self.device)
+            self._meta_generation += 1
         self._turn_used = turn
         return self._pinned[turn]
 
@@ -228,6 +234,11 @@ class Engine:
         max_kv = max(s.pos0 + s.n for s in segments)
         max_q = max(s.n for s in segments)
         width = max(1, -(-max_kv // P))
+        if max_q == 1:
+            # decode-only steps keep their metadata layout (and with it a
+            # captured graph) while contexts grow: the table width moves in
+            # steps of 8 pages
+            width = min(-(-width // 8) * 8, self.cache.max_pages_per_request)
         groups = self.cache.paged_groups
 
         # packed layout, every section 16-byte aligned
@@ -287,7 +298,8 @@ class Engine:
             decode_rows=sec("dec_rows", len(dec_rows)) if mixed else None,
             prefill_rows=sec("pre_rows", len(pre_rows)) if mixed else None,
             num_decode_rows=len(dec_rows), num_prefill_rows=len(pre_rows),
-            max_decode_kv_len=max((s.pos0 + 1 for s in segments if s.n == 1), default=0))
+            max_decode_kv_len=(width * P if max_q == 1 else
+                               max((s.pos0 + 1 for s in segments if s.n == 1), default=0)))
         in_order = N == T and rows == list(range(T))
         return ctx, sec("logit_rows", N), N, in_order
 
@@ -302,12 +314,49 @@ class Engine:
         self.last_meta_ints = self._last_meta_ints
         self.storage.clear_state(self.cache.take_fresh_slots())
         logits = self.workspace.get("engine.logits", (N, self.plan.vocab_size), torch.float32)
-        self.model.forward(ctx, self.cache_views, logit_rows, logits, in_order)
+        if not self._replay_graph(ctx, logit_rows, logits, N, in_order, probe):
+            self.model.forward(ctx, self.cache_views, logit_rows, logits, in_order)
         for e, seg in zip(entries, ctx.segments):
             self.cache.advance(e.request, seg.n)
         self.steps += 1
         self.tokens_run += ctx.num_tokens
         return logits
+
+    def _replay_graph(self, ctx: StepContext, logit_rows, logits, N: int, in_order: bool, probe) -> bool:
+        """Decode-only steps with every row's logits wanted run as a captured
+        CUDA graph (the reference captures its decode step per batch size,
+        python/freetoken/engine/graph.py:127-198).  A key is run eagerly once
+        (which also sizes every scratch buffer), captured at its second use
+        and replayed from then on.  Returns whether the step ran as a graph."""
+        T = ctx.num_tokens
+        if (probe is not None or not ctx.decode_only or not in_order or N != T
+                or T > self.args.cuda_graph_max_bs or self.dtype != torch.bfloat16
+                or self.cache.state_groups):
+            return False
+        key = (T, tuple(t.shape[1] for t in ctx.block_tables), self.workspace.generation,
+               self._meta_generation)
+        graph = self._graphs.get(key)
+        if graph is None:
+            seen = self._graph_seen.get(key, 0)
+            self._graph_seen[key] = seen + 1
+            if seen == 0:
+                return False
+            # drop graphs whose buffers were replaced
+            for old in [k for k in self._graphs if k[2:] != key[2:]]:
+                del self._graphs[old]
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, self.cache_views, logit_rows, logits, in_order)
+            kernels = ops.launch_count() - before
+            ops.LAUNCHES -= kernels          # recorded, not run
+            self._graphs[key] = (graph, kernels)
+            graph = self._graphs[key]
+        graph[0].replay()
+        ops.LAUNCHES += graph[1]
+        self.graph_replays += 1
+        return True
 
     # ---- reporting ---------------------------------------------------------------
     def stats(self) -> Dict[str, Any]:

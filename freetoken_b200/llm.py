@@ -4,7 +4,7 @@ In the reference's manner (python/freetoken/llm/llm.py:30-43,105-142):
 ``LLM(model_path, dtype=torch.bfloat16, **kwargs)`` with the scheduler's option
 names as keywords (``max_running_req``, ``page_size``, ``num_page_override``,
 ``max_extend_tokens``, ``max_seq_len_override``, ``memory_ratio``,
-``use_dummy_weight``; python/freetoken/engine/config.py:16-105,
+``use_dummy_weight``, ``cuda_graph_max_bs``; python/freetoken/engine/config.py:16-105,
 python/freetoken/scheduler/config.py:14-43), and
 ``generate(prompts, sampling_params) -> [{"text", "token_ids"}, ...]`` where
 prompts are token-id lists or, if the model folder has a tokenizer, strings.
@@ -50,7 +50,8 @@ class LLM:
                  max_running_req: int = 4, page_size: int = 64,
                  num_page_override: Optional[int] = None, num_token_override: Optional[int] = None,
                  max_extend_tokens: int = 8192, max_seq_len_override: Optional[int] = None,
-                 memory_ratio: float = 0.9, use_dummy_weight: bool = False, seed: int = 0,
+                 memory_ratio: float = 0.9, use_dummy_weight: bool = False,
+                 cuda_graph_max_bs: int = 64, seed: int = 0,
                  device: str = "cuda:0", config: Optional[Dict[str, Any]] = None):
         """``model_path``: a folder with ``config.json`` and safetensors files.
         With ``use_dummy_weight`` only ``config.json`` (or ``config``) is
@@ -58,7 +59,8 @@ class LLM:
         args = EngineArgs(dtype=dtype, device=device, page_size=page_size,
                           num_pages=num_page_override, max_tokens=num_token_override,
                           max_running_requests=max_running_req, max_seq_len=max_seq_len_override,
-                          memory_ratio=memory_ratio, max_step_tokens=max_extend_tokens)
+                          memory_ratio=memory_ratio, max_step_tokens=max_extend_tokens,
+                          cuda_graph_max_bs=cuda_graph_max_bs)
         raw: Dict[str, Any]
         if config is not None:
             raw = dict(config)

@@ -59,6 +59,9 @@ class Workspace:
     def __init__(self, device):
         self.device = torch.device(device)
         self._buffers: Dict[str, torch.Tensor] = {}
+        # bumped whenever a buffer is (re)allocated: captured CUDA graphs hold
+        # raw addresses and must be dropped then
+        self.generation = 0
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         count = 1
@@ -69,6 +72,7 @@ class Workspace:
             grow = max(count, 1)
             buf = torch.empty(grow, dtype=dtype, device=self.device)
             self._buffers[name] = buf
+            self.generation += 1
         return buf[:count].view(*shape)
 
     def bytes(self) -> int:

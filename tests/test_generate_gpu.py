@@ -1,0 +1,109 @@
+"""Generation through the Python entry point: greedy tokens equal to the plain
+implementation's greedy loop, long decoding (graph replay included), sampling."""
+
+import pytest
+import torch
+
+import tiny
+from plain_model import PlainModel
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folder_a(tmp_path_factory):
+    return tiny.write_tiny(str(tmp_path_factory.mktemp("genA")), "A")
+
+
+@pytest.fixture(scope="module")
+def folder_c(tmp_path_factory):
+    return tiny.write_tiny(str(tmp_path_factory.mktemp("genC")), "C")
+
+
+def test_greedy_generation_float32(folder_a):
+    """tiny-A workload: prompts of 5/9/17 tokens, 8 new tokens each, page size 4."""
+    from freetoken_b200 import LLM, SamplingParams
+    vocab = tiny.TINY_A["vocab_size"]
+    prompts = [tiny.tokens(s, n, vocab) for s, n in ((1, 5), (2, 9), (3, 17))]
+    llm = LLM(folder_a, "float32", page_size=4, num_token_override=96, max_running_req=3)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    plain = PlainModel(folder_a, "float32")
+    for prompt, result in zip(prompts, out):
+        assert result["token_ids"] == plain.greedy(prompt, 8)
+        assert result["finish_reason"] == "length"
+    llm.scheduler.check_integrity()
+    assert llm.engine.cache.free_pages() == llm.engine.cache.total_pages()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_matches_whole_sequence(folder_c, dtype):
+    """Decode 150 tokens one by one (graph replay in bfloat16), then run prompt +
+    generated tokens whole through a fresh engine: the logits that chose every
+    token must agree, and so must the greedy choice unless two logits tie."""
+    from freetoken_b200 import LLM, SamplingParams
+    from freetoken_b200.engine import Engine, EngineArgs, StepEntry
+    vocab = tiny.TINY_C["vocab_size"]
+    prompts = [tiny.tokens(5, 33, vocab), tiny.tokens(6, 7, vocab)]
+    llm = LLM(folder_c, dtype, page_size=16, num_token_override=512, max_running_req=2)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=150, ignore_eos=True))
+    if dtype == "bfloat16":
+        assert llm.engine.graph_replays > 100
+    engine = Engine.from_folder(folder_c, EngineArgs(dtype=dtype, page_size=16, max_tokens=512,
+                                                     max_running_requests=2))
+    for prompt, result in zip(prompts, out):
+        gen = result["token_ids"]
+        assert len(gen) == 150
+        seq = prompt + gen
+        logits = engine.step([StepEntry("w", seq[:-1], list(range(len(prompt) - 1, len(seq) - 1)))])
+        engine.end_request("w")
+        logits = logits.float().cpu()
+        top2 = logits.topk(2, dim=-1).values
+        clear = (top2[:, 0] - top2[:, 1]) > (1e-4 if dtype == "float32" else 5e-2)
+        greedy = logits.argmax(-1)
+        agree = greedy == torch.tensor(gen)
+        assert agree[clear].all(), f"decoded tokens differ from whole-sequence greedy at {(~agree & clear).nonzero().flatten().tolist()}"
+
+
+def test_first_tokens_of_a_sequence(folder_a):
+    """Positions 0 and 1: one key, no history, first slot of the first page."""
+    from freetoken_b200.engine import Engine, EngineArgs, StepEntry
+    plain = PlainModel(folder_a, "float32")
+    engine = Engine.from_folder(folder_a, EngineArgs(dtype="float32", page_size=4, max_tokens=16,
+                                                     max_running_requests=2))
+    toks = tiny.tokens(9, 3, tiny.TINY_A["vocab_size"])
+    want = plain.forward(toks)
+    got0 = engine.step([StepEntry("a", toks[:1], [0])]).cpu().clone()
+    got1 = engine.step([StepEntry("a", toks[1:2], [0])]).cpu().clone()
+    got2 = engine.step([StepEntry("a", toks[2:3], [0])]).cpu().clone()
+    assert torch.allclose(torch.cat([got0, got1, got2]), want, **tiny.TOL["float32"])
+
+
+def test_temperature_sampling_is_reproducible_and_batch_independent(folder_a):
+    """tiny-B style workload: temperature 0.8, seeds per request; a request's
+    tokens do not depend on what else is in the batch."""
+    from freetoken_b200 import LLM, SamplingParams
+    vocab = tiny.TINY_A["vocab_size"]
+    prompts = [tiny.tokens(s, n, vocab) for s, n in ((1, 1), (2, 6), (3, 13), (4, 31))]
+    params = [SamplingParams(temperature=0.8, max_tokens=6, ignore_eos=True, seed=3 + i) for i in range(4)]
+    llm = LLM(folder_a, "float32", page_size=8, num_token_override=256, max_running_req=4,
+              max_extend_tokens=7)
+    together = llm.generate(prompts, params)
+    again = llm.generate(prompts, params)
+    assert [r["token_ids"] for r in together] == [r["token_ids"] for r in again]
+    alone = [llm.generate([p], [sp])[0] for p, sp in zip(prompts, params)]
+    assert [r["token_ids"] for r in together] == [r["token_ids"] for r in alone]
+    assert any(r["token_ids"] != llm.generate([p], SamplingParams(max_tokens=6, ignore_eos=True))[0]["token_ids"]
+               for r, p in zip(together, prompts)), "temperature sampling never left the greedy path"
+
+
+def test_eos_stops_generation(folder_a):
+    from freetoken_b200 import LLM, SamplingParams
+    vocab = tiny.TINY_A["vocab_size"]
+    prompt = tiny.tokens(1, 5, vocab)
+    llm = LLM(folder_a, "float32", page_size=4, num_token_override=64, max_running_req=1)
+    free = llm.generate([prompt], SamplingParams(max_tokens=8, ignore_eos=True))[0]["token_ids"]
+    stop_at = free[3]
+    if stop_at in free[:3]:
+        pytest.skip("the chosen stop token appears earlier")
+    out = llm.generate([prompt], SamplingParams(max_tokens=8, stop_token_ids=[stop_at]))[0]
+    assert out["token_ids"] == free[:3] and out["finish_reason"] == "stop"
