@@ -32,19 +32,23 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __res
 
 // ------------------------------------------------------------------ rmsnorm
 // residual (float32) is updated in place with delta when delta != nullptr.
+// delta holds k rows per token (k > 1: the partial results of a token's k
+// routes); they are added in ascending order in float32, then to the residual.
 template <typename AT>
 __global__ void rmsnorm_kernel(const AT* __restrict__ delta, float* __restrict__ residual,
                                const float* __restrict__ weight, AT* __restrict__ out, int H,
-                               float eps, int plus_one) {
+                               float eps, int plus_one, int k) {
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   float* r = residual + (size_t)t * H;
-  const AT* d = delta ? delta + (size_t)t * H : nullptr;
+  const AT* d = delta ? delta + (size_t)t * k * H : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float z = r[i];
     if (d) {
-      z += to_float(d[i]);
+      float add = to_float(d[i]);
+      for (int j = 1; j < k; ++j) add += to_float(d[(size_t)j * H + i]);
+      z += add;
       r[i] = z;
     }
     ss += z * z;
@@ -176,6 +180,128 @@ __global__ void qk_rope_store_kernel(QkRopeArgs a) {
   }
 }
 
+// Same work for bfloat16 rows in 16-byte pieces: head_dim % 8 == 0, NeoX
+// pairing with rotary_dim % 16 == 0, so that a piece of 8 elements below R/2
+// pairs with the piece R/2 further on.
+struct Chunk8 { float v[8]; };
+__device__ __forceinline__ Chunk8 load8(const __nv_bfloat16* p) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  Chunk8 c;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    c.v[2 * i] = f.x;
+    c.v[2 * i + 1] = f.y;
+  }
+  return c;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const Chunk8& c) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(c.v[2 * i], c.v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+__device__ __forceinline__ float sumsq8(const Chunk8& c) {
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += c.v[i] * c.v[i];
+  return s;
+}
+
+__global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
+  extern __shared__ float head_inv[];
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const __nv_bfloat16* row = (const __nv_bfloat16*)a.qkv + (size_t)t * a.ld;
+  const int d = a.d, dc = d >> 3;                 // pieces per head
+  const int qn = a.nq * d, kn = a.nkv * d;
+  float inv_q = 1.f, inv_k = 1.f;
+  if (a.norm_mode == 1) {
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < (qn >> 3); c += blockDim.x) sq += sumsq8(load8(row + c * 8));
+    for (int c = threadIdx.x; c < (kn >> 3); c += blockDim.x) sk += sumsq8(load8(row + qn + c * 8));
+    inv_q = rsqrtf(block_sum(sq, scratch) / (float)qn + a.eps);
+    inv_k = rsqrtf(block_sum(sk, scratch) / (float)kn + a.eps);
+  } else if (a.norm_mode == 2) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int h = warp; h < a.nq + a.nkv; h += nwarps) {
+      float s = 0.f;
+      for (int c = lane; c < dc; c += 32) s += sumsq8(load8(row + (size_t)h * d + c * 8));
+      s = warp_sum(s);
+      if (lane == 0) head_inv[h] = rsqrtf(s / (float)d + a.eps);
+    }
+    __syncthreads();
+  }
+  const int pos = a.token_pos[t];
+  const int half = a.R >> 1, hc = half >> 3;      // rotary half, in pieces
+  const float* cs = (a.cos_sin && a.R > 0) ? a.cos_sin + (size_t)pos * a.R : nullptr;
+  const float one = a.plus_one ? 1.f : 0.f;
+  __nv_bfloat16* qo = (__nv_bfloat16*)a.q_out + (size_t)t * qn;
+  __nv_bfloat16* ko = nullptr;
+  __nv_bfloat16* vo = nullptr;
+  if (a.kv_pages) {
+    const int seg = a.token_seg[t];
+    const int page = a.block_table[(size_t)seg * a.table_width + pos / a.P];
+    const size_t base = (size_t)page * a.page_stride + (size_t)(pos % a.P) * d;
+    ko = (__nv_bfloat16*)a.kv_pages + base;
+    vo = (__nv_bfloat16*)a.kv_pages + a.kv_stride + base;
+  }
+  const size_t head_stride_cache = (size_t)a.P * d;
+  const int per_head = dc - hc;                   // work items per head
+  const int total_q = a.nq * per_head, total = total_q + a.nkv * per_head;
+  for (int w = threadIdx.x; w < total; w += blockDim.x) {
+    const bool is_q = w < total_q;
+    const int ww = is_q ? w : w - total_q;
+    const int h = ww / per_head, ci = ww % per_head;
+    if (!is_q && !ko) continue;
+    const __nv_bfloat16* src = row + (is_q ? 0 : qn) + (size_t)h * d;
+    __nv_bfloat16* dst = is_q ? qo + (size_t)h * d : ko + (size_t)h * head_stride_cache;
+    const float* nw = is_q ? a.q_weight : a.k_weight;
+    float inv = 1.f;
+    if (a.norm_mode == 1) inv = is_q ? inv_q : inv_k;
+    if (a.norm_mode == 2) inv = head_inv[is_q ? h : a.nq + h];
+    const int wbase = a.norm_mode == 1 ? h * d : 0;
+    if (ci < hc) {
+      const int i0 = ci * 8, i1 = i0 + half;
+      Chunk8 x0 = load8(src + i0), x1 = load8(src + i1);
+      if (a.norm_mode) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          x0.v[i] = x0.v[i] * inv * (nw[wbase + i0 + i] + one);
+          x1.v[i] = x1.v[i] * inv * (nw[wbase + i1 + i] + one);
+        }
+      }
+      Chunk8 y0, y1;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float c = cs ? cs[i0 + i] : 1.f, sn = cs ? cs[half + i0 + i] : 0.f;
+        y0.v[i] = x0.v[i] * c - x1.v[i] * sn;
+        y1.v[i] = x1.v[i] * c + x0.v[i] * sn;
+      }
+      store8(dst + i0, y0);
+      store8(dst + i1, y1);
+    } else {
+      const int i0 = (ci + hc) * 8;               // pieces beyond the rotary span
+      Chunk8 x0 = load8(src + i0);
+      if (a.norm_mode) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x0.v[i] = x0.v[i] * inv * (nw[wbase + i0 + i] + one);
+      }
+      store8(dst + i0, x0);
+    }
+  }
+  if (vo) {
+    const __nv_bfloat16* v = row + qn + kn;
+    for (int c = threadIdx.x; c < (kn >> 3); c += blockDim.x) {
+      const int h = (c * 8) / d, i = (c * 8) % d;
+      *reinterpret_cast<uint4*>(vo + (size_t)h * head_stride_cache + i) =
+          *reinterpret_cast<const uint4*>(v + c * 8);
+    }
+  }
+}
+
 // --------------------------------------------------------------- top-k sum
 // out[t,:] = sum_j parts[t*k+j,:] in float32, j ascending.
 template <typename AT>
@@ -214,11 +340,12 @@ int ft_embed_gather(const int* ids, const void* table, int table_dtype, float* r
 }
 
 int ft_rmsnorm(const void* delta, float* residual, const float* weight, void* out, int dtype,
-               int T, int H, float eps, int plus_one, cudaStream_t stream) {
+               int T, int H, float eps, int plus_one, int k, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
+  if (k < 1) return FT_ERR_SHAPE;
   FT_DISPATCH(dtype, AT,
               rmsnorm_kernel<AT><<<T, 256, 0, stream>>>((const AT*)delta, residual, weight,
-                                                        (AT*)out, H, eps, plus_one));
+                                                        (AT*)out, H, eps, plus_one, k));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -235,6 +362,14 @@ int ft_qk_rope_store(const void* qkv, void* q_out, void* kv_pages, const float* 
                block_table, ld, page_stride, kv_stride, nq, nkv, d, R, P, table_width,
                norm_mode, plus_one, interleaved, eps};
   const size_t smem = (size_t)(nq + nkv) * sizeof(float);
+  const bool aligned = !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) &&
+                       !((uintptr_t)kv_pages & 15) && !(ld & 7) && !(page_stride & 7) &&
+                       !(kv_stride & 7);
+  if (dtype == FT_DTYPE_BF16 && aligned && !(d & 7) && !(R & 15) && !interleaved) {
+    qk_rope_store_vec_kernel<<<T, 256, smem, stream>>>(a);
+    FT_LAUNCH_CHECK();
+    return FT_OK;
+  }
   FT_DISPATCH(dtype, AT, qk_rope_store_kernel<AT><<<T, 256, smem, stream>>>(a));
   FT_LAUNCH_CHECK();
   return FT_OK;

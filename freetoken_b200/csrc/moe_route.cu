@@ -75,23 +75,47 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
 }
 
 // Router logits for few tokens: one warp per expert row.  logits[t,e] =
-// sum_h x[t,h] * W[e,h] in float32; a lane sums its strided share in ascending
-// h, lanes are added by an xor-shuffle tree - the same arithmetic for a token
-// whatever else is in the launch.
+// sum_h x[t,h] * W[e,h] in float32.  The row of W is walked in chunks of 256
+// (8 values per lane, kept in registers) against 8 tokens at a time; a lane
+// sums its share in ascending h, lanes are added by an xor-shuffle tree - the
+// same arithmetic for a token whatever else is in the launch.
 template <typename AT>
 __global__ void router_logits_kernel(const AT* __restrict__ x, long long ldx,
                                      const float* __restrict__ W, float* __restrict__ logits,
                                      int T, int E, int H) {
+  constexpr int TT = 8;
   const int lane = threadIdx.x & 31;
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (e >= E) return;
   const float* w = W + (size_t)e * H;
-  for (int t = 0; t < T; ++t) {
-    const AT* xr = x + (size_t)t * ldx;
-    float s = 0.f;
-    for (int h = lane; h < H; h += 32) s = fmaf(to_float(xr[h]), w[h], s);
-    s = warp_sum(s);
-    if (lane == 0) logits[(size_t)t * E + e] = s;
+  for (int t0 = 0; t0 < T; t0 += TT) {
+    float acc[TT];
+#pragma unroll
+    for (int i = 0; i < TT; ++i) acc[i] = 0.f;
+    for (int h0 = 0; h0 < H; h0 += 256) {
+      float wv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int h = h0 + i * 32 + lane;
+        wv[i] = h < H ? w[h] : 0.f;
+      }
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) {
+        if (t0 + tt < T) {
+          const AT* xr = x + (size_t)(t0 + tt) * ldx;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int h = h0 + i * 32 + lane;
+            if (h < H) acc[tt] = fmaf(to_float(xr[h]), wv[i], acc[tt]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+      const float v = warp_sum(acc[tt]);
+      if (lane == 0 && t0 + tt < T) logits[(size_t)(t0 + tt) * E + e] = v;
+    }
   }
 }
 
@@ -110,23 +134,35 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int* __restrict__ 
 }
 
 // offsets[e] = sum counts[<e]; sorted_route[offsets[e] + i] = i-th route of
-// expert e in ascending route order; sorted_token = sorted_route / k.
+// expert e in ascending route order; sorted_token = sorted_route / k;
+// active[j] = j-th expert that has routes (ascending), active[E] = how many.
 __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ counts,
                                    int* __restrict__ offsets, int* __restrict__ sorted_route,
-                                   int* __restrict__ sorted_token, int R, int E, int k) {
+                                   int* __restrict__ sorted_token, int* __restrict__ active,
+                                   int R, int E, int k) {
   const int lane = threadIdx.x & 31;
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (e >= E) return;
-  int before = 0;
+  int before = 0, busy_before = 0;
   for (int base = 0; base < e; base += 32) {
     const int i = base + lane;
-    before += i < e ? counts[i] : 0;
+    const int c = i < e ? counts[i] : 0;
+    before += c;
+    busy_before += c > 0;
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+  for (int o = 16; o > 0; o >>= 1) {
+    before += __shfl_xor_sync(0xffffffffu, before, o);
+    busy_before += __shfl_xor_sync(0xffffffffu, busy_before, o);
+  }
   if (lane == 0) {
+    const int mine = counts[e];
     offsets[e] = before;
-    if (e == E - 1) offsets[E] = before + counts[e];
+    if (mine > 0) active[busy_before] = e;
+    if (e == E - 1) {
+      offsets[E] = before + mine;
+      active[E] = busy_before + (mine > 0);
+    }
   }
   int at = before;
   for (int base = 0; base < R; base += 32) {
@@ -176,13 +212,13 @@ int ft_router_logits(const void* x, int x_dtype, long long ldx, const float* W, 
 }
 
 int ft_moe_sort(const int* ids, int* counts, int* offsets, int* sorted_route, int* sorted_token,
-                int R, int E, int k, cudaStream_t stream) {
+                int* active, int R, int E, int k, cudaStream_t stream) {
   if (R <= 0) return FT_OK;
   const int warps = 4;
   const int blocks = (E + warps - 1) / warps;
   moe_count_kernel<<<blocks, warps * 32, 0, stream>>>(ids, counts, R, E);
   moe_scatter_kernel<<<blocks, warps * 32, 0, stream>>>(ids, counts, offsets, sorted_route,
-                                                        sorted_token, R, E, k);
+                                                        sorted_token, active, R, E, k);
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

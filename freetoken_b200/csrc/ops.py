@@ -105,20 +105,25 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor)
 
 def rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor,
             out: torch.Tensor, eps: float, plus_one: bool) -> None:
-    """residual += delta (if given); out = residual * rsqrt(mean(residual^2)+eps) * (weight [+1])"""
+    """residual += delta (if given); out = residual * rsqrt(mean(residual^2)+eps) * (weight [+1]).
+
+    ``delta`` may be ``[T, k, H]``: k partial rows per token, added in order."""
     _need(residual, "residual", torch.float32)
     _need(weight, "weight", torch.float32)
     _need(out, "out")
     T, H = residual.shape
+    k = 1
     if delta is not None:
         _need(delta, "delta", out.dtype)
-        if delta.shape != residual.shape:
-            raise KernelError("rmsnorm: delta and residual differ in shape")
+        if delta.dim() == 3:
+            k = delta.shape[1]
+        if delta.shape[0] != T or delta.shape[-1] != H or delta.dim() not in (2, 3):
+            raise KernelError("rmsnorm: delta must be [T, H] or [T, k, H]")
     if out.shape != residual.shape or weight.numel() != H:
         raise KernelError("rmsnorm: shapes do not match")
-    f = _fn("elementwise", "ft_rmsnorm", "p p p p i i i f i")
+    f = _fn("elementwise", "ft_rmsnorm", "p p p p i i i f i i")
     _check(f(_ptr(delta), _ptr(residual), _ptr(weight), _ptr(out), code(out.dtype), T, H,
-             float(eps), int(plus_one), _stream()), "rmsnorm")
+             float(eps), int(plus_one), k, _stream()), "rmsnorm")
 
 
 def qk_rope_store(qkv: torch.Tensor, q_out: torch.Tensor, kv_pages: Optional[torch.Tensor],
@@ -235,7 +240,8 @@ def skinny_gemm_takes(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool
 
 
 def skinny_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
-                group_offsets: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
+                group_offsets: Optional[torch.Tensor] = None,
+                active: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None,
                 c_rows: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
                 rows: Optional[int] = None, glu: bool = False, act: str = "silu",
                 act_alpha: float = 1.702, act_limit: float = 7.0, rows_per_pass: int = 8) -> None:
@@ -258,9 +264,13 @@ def skinny_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
         raise KernelError("skinny_gemm: group_offsets must be given exactly for grouped weights")
     if rows_per_pass not in (8, 16, 32):
         raise KernelError("skinny_gemm: rows_per_pass must be 8, 16 or 32")
-    f = _fn("skinny_gemm", "ft_skinny_gemm", "p q p q p i q p p p p i i i i i i f f i")
+    if active is not None:
+        _need(active, "active", torch.int32)
+        if active.numel() < G + 1:
+            raise KernelError("skinny_gemm: the active list needs G + 1 entries")
+    f = _fn("skinny_gemm", "ft_skinny_gemm", "p q p q p i q p p p p p i i i i i i f f i")
     _check(f(_ptr(a), a.stride(0), _ptr(w), NW * K, _ptr(c), code(c.dtype), c.stride(0),
-             _ptr(group_offsets), _ptr(a_rows), _ptr(c_rows), _ptr(row_scale), M, N, K, G,
+             _ptr(group_offsets), _ptr(active), _ptr(a_rows), _ptr(c_rows), _ptr(row_scale), M, N, K, G,
              int(glu), 0 if act == "silu" else 1, float(act_alpha), float(act_limit),
              rows_per_pass, _stream()), "skinny_gemm")
 
@@ -377,19 +387,22 @@ def router_logits(x: torch.Tensor, w: torch.Tensor, logits: torch.Tensor) -> Non
 
 
 def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor,
-             sorted_route: torch.Tensor, sorted_token: torch.Tensor, num_experts: int,
-             k: int) -> None:
-    """Stable counting sort of the ``T*k`` routes by expert."""
+             sorted_route: torch.Tensor, sorted_token: torch.Tensor, active: torch.Tensor,
+             num_experts: int, k: int) -> None:
+    """Stable counting sort of the ``T*k`` routes by expert; ``active`` gets the
+    experts that have routes (ascending) and, at index ``num_experts``, their number."""
     for name, t in (("ids", ids), ("counts", counts), ("offsets", offsets),
-                    ("sorted_route", sorted_route), ("sorted_token", sorted_token)):
+                    ("sorted_route", sorted_route), ("sorted_token", sorted_token),
+                    ("active", active)):
         _need(t, name, torch.int32)
     R = ids.numel()
     if counts.numel() < num_experts or offsets.numel() < num_experts + 1 \
-            or sorted_route.numel() < R or sorted_token.numel() < R:
+            or sorted_route.numel() < R or sorted_token.numel() < R \
+            or active.numel() < num_experts + 1:
         raise KernelError("moe_sort: output buffers are too small")
-    f = _fn("moe_route", "ft_moe_sort", "p p p p p i i i")
-    _check(f(_ptr(ids), _ptr(counts), _ptr(offsets), _ptr(sorted_route), _ptr(sorted_token), R,
-             num_experts, k, _stream()), "moe_sort")
+    f = _fn("moe_route", "ft_moe_sort", "p p p p p p i i i")
+    _check(f(_ptr(ids), _ptr(counts), _ptr(offsets), _ptr(sorted_route), _ptr(sorted_token),
+             _ptr(active), R, num_experts, k, _stream()), "moe_sort")
 
 
 # -------------------------------------------------------------- sampling

@@ -13,8 +13,9 @@
 // A block is 4 warps that split K four ways over the same 16 weight rows and
 // add their partial sums in warp order through shared memory, so a result does
 // not depend on the launch shape.  Grouped use (experts): blockIdx.y is the
-// expert, rows group_offsets[e]..group_offsets[e+1] of the sorted routes are
-// its tokens, taken 8*NT at a time; experts without tokens exit at once.
+// j-th expert that has tokens (from the `active` list, so the grid is no larger
+// than the number of routes), rows group_offsets[e]..group_offsets[e+1] of the
+// sorted routes are its tokens, taken 8*NT at a time.
 //
 // Reference counterpart: python/freetoken/kernel/triton/decode_moe.py:5-75 (one
 // program per route, CUDA-core FMAs: an expert's weights are read once per
@@ -29,11 +30,12 @@ struct SkinnyArgs {
   const __nv_bfloat16* W;
   void* C;
   const int* group_offsets;  // [G+1] or nullptr
+  const int* active;         // [G+1]: groups that have rows, then their number; or nullptr
   const int* a_rows;         // sorted row -> row of A, or nullptr
   const int* c_rows;         // sorted row -> row of C, or nullptr
   const float* row_scale;    // by row of C, or nullptr
   long long lda, ldc, w_group_stride;
-  int M, N, K;
+  int M, N, K, G;
   int act;
   float act_alpha, act_limit;
 };
@@ -70,7 +72,11 @@ __global__ void __launch_bounds__(KS * 32) skinny_kernel(SkinnyArgs a) {
   constexpr int NG = GLU ? 2 : 1;
   __shared__ float red[KS][NT][NG][16][8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int group = blockIdx.y;
+  int group = blockIdx.y;
+  if (a.active) {
+    if ((int)blockIdx.y >= a.active[a.G]) return;
+    group = a.active[blockIdx.y];
+  }
   int row_begin = 0, row_end = a.M;
   if (a.group_offsets) {
     row_begin = a.group_offsets[group];
@@ -196,17 +202,18 @@ using namespace ft;
 // lda % 8 == 0 and 16-byte aligned base pointers; refuses anything else.
 extern "C" int ft_skinny_gemm(const void* A, long long lda, const void* W,
                               long long w_group_stride, void* C, int c_dtype, long long ldc,
-                              const int* group_offsets, const int* a_rows, const int* c_rows,
-                              const float* row_scale, int M, int N, int K, int G, int glu,
+                              const int* group_offsets, const int* active, const int* a_rows,
+                              const int* c_rows, const float* row_scale, int M, int N, int K, int G, int glu,
                               int act, float act_alpha, float act_limit, int rows_per_pass,
                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return FT_OK;
   if (K <= 0 || (K & 7) || (lda & 7) || G <= 0) return FT_ERR_SHAPE;
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((w_group_stride * 2) & 15)) return FT_ERR_SHAPE;
   if (G > 65535) return FT_ERR_SHAPE;
-  SkinnyArgs a{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, C, group_offsets, a_rows, c_rows,
-               row_scale, lda, ldc, w_group_stride, M, N, K, act, act_alpha, act_limit};
-  dim3 grid((N + 15) / 16, G);
+  SkinnyArgs a{(const __nv_bfloat16*)A, (const __nv_bfloat16*)W, C, group_offsets, active, a_rows,
+               c_rows, row_scale, lda, ldc, w_group_stride, M, N, K, G, act, act_alpha, act_limit};
+  // with the list of busy groups, no more groups than rows can have any
+  dim3 grid((N + 15) / 16, active ? min(G, M) : G);
   const int nt = rows_per_pass / 8;
   int rc;
   if (c_dtype == FT_DTYPE_BF16) {

@@ -8,13 +8,14 @@ in: names of tensors, sizes and options all arrive as parameters.
 Kinds of parts and what each must offer:
 
 * **Norm**          ``forward(ctx, delta, residual) -> normed``.  Adds ``delta``
-  (may be ``None``) into the float32 ``residual`` in place and returns the
-  normalised rows in the activation dtype.
+  (``[T, H]``, ``[T, k, H]`` or ``None``) into the float32 ``residual`` in place
+  and returns the normalised rows in the activation dtype.
 * **Position**      tables or constants a mixer applies to queries and keys.
 * **Mixer**         ``cache_need()`` says what the cache manager must keep for
   it (paged keys/values, a fixed-size state, or nothing);
   ``forward(ctx, x, cache) -> y`` mixes the tokens of each request in order.
-* **FeedForward**   ``forward(ctx, x) -> y``, token by token.
+* **FeedForward**   ``forward(ctx, x) -> y``, token by token.  ``y`` is ``[T, H]``
+  or ``[T, k, H]``: k partial rows per token that the next norm adds in order.
 * **Block**         arranges a mixer, a feed-forward and their norms around the
   residual stream: ``forward(ctx, delta, residual, cache) -> delta``.
 * **Embedding / Head**  token ids -> residual rows; normed rows -> logits.

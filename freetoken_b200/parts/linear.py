@@ -25,14 +25,37 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Te
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         rows = x.shape[0]
         takes = ops.skinny_gemm_takes(x, weight, out)
-        if takes and (rows <= SKINNY_ROWS or out.dtype != torch.bfloat16):
+        if takes and rows <= SKINNY_ROWS:
             ops.skinny_gemm(x, weight, out, rows_per_pass=ops.pass_rows(rows))
             return out
         if out.dtype == torch.bfloat16:
             torch.matmul(x, weight.t(), out=out)
             return out
+        if out.dtype == torch.float32 and _library_f32_out(x, weight, out):
+            return out
+        if takes:
+            ops.skinny_gemm(x, weight, out, rows_per_pass=32)
+            return out
     ops.gemm_rows(x, weight, out)
     return out
+
+
+_F32_OUT = {"ok": None}
+
+
+def _library_f32_out(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
+    """bfloat16 x bfloat16 -> float32 through the library product, where this
+    PyTorch offers it (``torch.mm(..., out_dtype=)``); the result is the
+    float32 accumulator, not a rounded bfloat16."""
+    if _F32_OUT["ok"] is False:
+        return False
+    try:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        _F32_OUT["ok"] = True
+        return True
+    except (TypeError, RuntimeError):
+        _F32_OUT["ok"] = False
+        return False
 
 
 # Up to this many rows the weight-streaming kernel reads the weights once;

@@ -114,7 +114,8 @@ class RoutedExperts(FeedForward):
         offsets = ws.get("moe.offsets", (self.E + 1,), torch.int32)
         sorted_route = ws.get("moe.sorted_route", (R,), torch.int32)
         sorted_token = ws.get("moe.sorted_token", (R,), torch.int32)
-        ops.moe_sort(ids.view(-1), counts, offsets, sorted_route, sorted_token, self.E, self.k)
+        active = ws.get("moe.active", (self.E + 1,), torch.int32)
+        ops.moe_sort(ids.view(-1), counts, offsets, sorted_route, sorted_token, active, self.E, self.k)
         if ctx.probe is not None:
             if "router_ids" in ctx.probe:
                 ctx.probe["router_ids"].append(ids.clone())
@@ -122,19 +123,22 @@ class RoutedExperts(FeedForward):
                 ctx.probe.setdefault("experts_touched", []).append(int((counts > 0).sum()))
         mid = ws.get("moe.mid", (R, self.inter), ctx.dtype)
         parts = ws.get("moe.parts", (R, self.hidden), ctx.dtype)
-        self.experts(ctx, x, mid, parts, offsets, sorted_route, sorted_token, weights.view(-1), R)
-        out = ws.get("moe.out", (T, self.hidden), ctx.dtype)
-        ops.combine(parts, out, self.k)
-        return out
+        self.experts(ctx, x, mid, parts, offsets, active, sorted_route, sorted_token,
+                     weights.view(-1), R)
+        # the k partial rows of a token are summed by whoever consumes them
+        # (the next norm adds them into the residual in slot order)
+        return parts.view(T, self.k, self.hidden)
 
-    def experts(self, ctx, x, mid, parts, offsets, sorted_route, sorted_token, route_weight, R):
+    def experts(self, ctx, x, mid, parts, offsets, active, sorted_route, sorted_token, route_weight, R):
         if ctx.dtype == torch.bfloat16 and ops.skinny_gemm_takes(x, self.w_gate_up, mid) \
                 and ops.skinny_gemm_takes(mid, self.w_down, parts):
             per_pass = ops.pass_rows(-(-R // self.E))
-            ops.skinny_gemm(x, self.w_gate_up, mid, group_offsets=offsets, a_rows=sorted_token,
+            ops.skinny_gemm(x, self.w_gate_up, mid, group_offsets=offsets, active=active,
+                            a_rows=sorted_token,
                             rows=R, glu=True, act=self.act, act_alpha=self.act_alpha,
                             act_limit=self.act_limit, rows_per_pass=per_pass)
-            ops.skinny_gemm(mid, self.w_down, parts, group_offsets=offsets, c_rows=sorted_route,
+            ops.skinny_gemm(mid, self.w_down, parts, group_offsets=offsets, active=active,
+                            c_rows=sorted_route,
                             row_scale=route_weight, rows=R, rows_per_pass=per_pass)
             return
         ops.gemm_rows(x, self.w_gate_up, mid, group_offsets=offsets, a_rows=sorted_token, rows=R,

@@ -53,6 +53,14 @@ def test_rmsnorm_residual(dtype, H, plus_one, eps):
     res2 = res_in.clone()
     ops().rmsnorm(None, res2, w, out, eps, plus_one)
     assert torch.equal(res2, res_in)
+    # k partial rows per token are summed in order
+    parts = rnd(T, 3, H, dtype=DT[dtype], seed=9)
+    res3 = res_in.clone()
+    ops().rmsnorm(parts, res3, w, out, eps, plus_one)
+    z3 = res_in + parts.float().sum(1)
+    want3 = z3 * torch.rsqrt(z3.pow(2).mean(-1, keepdim=True) + eps) * (w + (1.0 if plus_one else 0.0))
+    assert torch.allclose(res3, z3, atol=1e-5)
+    assert torch.allclose(out.float(), want3, **TOL[dtype])
 
 
 def _rope_ref(x, pos, R, theta, interleaved):
@@ -77,7 +85,8 @@ def _rope_ref(x, pos, R, theta, interleaved):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nq,nkv,d,R,mode,interleaved,P", [
     (4, 2, 16, 8, 1, False, 4), (6, 3, 24, 24, 0, False, 8), (12, 2, 32, 16, 2, True, 16),
-    (5, 5, 48, 0, 2, False, 2), (48, 8, 128, 64, 1, False, 64)])
+    (5, 5, 48, 0, 2, False, 2), (48, 8, 128, 64, 1, False, 64), (12, 4, 64, 32, 2, False, 16),
+    (8, 2, 32, 32, 0, False, 8), (6, 2, 40, 16, 1, False, 8)])
 def test_qk_rope_store(dtype, nq, nkv, d, R, mode, interleaved, P):
     o = ops()
     T, S, theta, eps = 9, 2, 12345.0, 1e-5
@@ -188,8 +197,11 @@ def test_expert_gemms(kernel, E, k, T, H, I, act):
     parts = torch.zeros(R, H, dtype=dt, device=DEV)
     if kernel == "skinny":
         per = o.pass_rows(-(-R // E))
-        o.skinny_gemm(x, w1, mid, group_offsets=offsets, a_rows=sorted_token, rows=R, glu=True,
-                      act=act, rows_per_pass=per)
+        busy = (offsets[1:] > offsets[:-1]).nonzero().flatten().to(torch.int32)
+        active = torch.cat([busy, torch.zeros(E - busy.numel(), dtype=torch.int32, device=DEV),
+                            torch.tensor([busy.numel()], dtype=torch.int32, device=DEV)])
+        o.skinny_gemm(x, w1, mid, group_offsets=offsets, active=active, a_rows=sorted_token,
+                      rows=R, glu=True, act=act, rows_per_pass=per)
         o.skinny_gemm(mid, w2, parts, group_offsets=offsets, c_rows=sorted_route, row_scale=rw,
                       rows=R, rows_per_pass=per)
     else:
@@ -331,7 +343,11 @@ def test_moe_sort_is_stable_counting_sort(E, k, T):
     offsets = torch.empty(E + 1, dtype=torch.int32, device=DEV)
     sr = torch.empty(R, dtype=torch.int32, device=DEV)
     st = torch.empty(R, dtype=torch.int32, device=DEV)
-    ops().moe_sort(ids.view(-1), counts, offsets, sr, st, E, k)
+    active = torch.full((E + 1,), -1, dtype=torch.int32, device=DEV)
+    ops().moe_sort(ids.view(-1), counts, offsets, sr, st, active, E, k)
+    busy = (want_off[1:] > want_off[:-1]).nonzero().flatten().to(torch.int32)
+    assert int(active[E]) == busy.numel()
+    assert torch.equal(active[:busy.numel()], busy)
     assert torch.equal(offsets, want_off)
     assert torch.equal(sr, want_route)
     assert torch.equal(st, want_token)
