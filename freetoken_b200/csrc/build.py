@@ -41,8 +41,9 @@ LIBRARIES: Dict[str, str] = {
     "sampling": "sampling.cu",
     "skinny_gemm": "skinny_gemm.cu",
     "attention_decode": "attention_decode.cu",
+    "attention_prefill": "attention_prefill.cu",
 }
-HEADERS: List[str] = ["common.cuh"]
+HEADERS: List[str] = ["common.cuh", "mma_utils.cuh"]
 EXTRA_LINK: Dict[str, List[str]] = {}
 
 

@@ -74,11 +74,28 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   }
 }
 
-// Router logits for few tokens: one warp per expert row.  logits[t,e] =
-// sum_h x[t,h] * W[e,h] in float32.  The row of W is walked in chunks of 256
-// (8 values per lane, kept in registers) against 8 tokens at a time; a lane
-// sums its share in ascending h, lanes are added by an xor-shuffle tree - the
-// same arithmetic for a token whatever else is in the launch.
+// Router logits for few tokens.  logits[t,e] = sum_h x[t,h] * W[e,h] in
+// float32.  One warp owns an expert row and 8 tokens; the row is walked in
+// pieces of 256 (a lane holds 8 consecutive values) against the 8 tokens'
+// matching pieces; a lane sums its share in ascending h, lanes are added by an
+// xor-shuffle tree - the same arithmetic for a token whatever else is in the
+// launch.  Needs H % 8 == 0 and 16-byte aligned rows.
+__device__ __forceinline__ void load8f(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8f(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
 template <typename AT>
 __global__ void router_logits_kernel(const AT* __restrict__ x, long long ldx,
                                      const float* __restrict__ W, float* __restrict__ logits,
@@ -86,38 +103,33 @@ __global__ void router_logits_kernel(const AT* __restrict__ x, long long ldx,
   constexpr int TT = 8;
   const int lane = threadIdx.x & 31;
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int t0 = blockIdx.y * TT;
   if (e >= E) return;
   const float* w = W + (size_t)e * H;
-  for (int t0 = 0; t0 < T; t0 += TT) {
-    float acc[TT];
+  float acc[TT];
 #pragma unroll
-    for (int i = 0; i < TT; ++i) acc[i] = 0.f;
-    for (int h0 = 0; h0 < H; h0 += 256) {
-      float wv[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int h = h0 + i * 32 + lane;
-        wv[i] = h < H ? w[h] : 0.f;
-      }
-#pragma unroll
-      for (int tt = 0; tt < TT; ++tt) {
-        if (t0 + tt < T) {
-          const AT* xr = x + (size_t)(t0 + tt) * ldx;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int h = h0 + i * 32 + lane;
-            if (h < H) acc[tt] = fmaf(to_float(xr[h]), wv[i], acc[tt]);
-          }
-        }
-      }
-    }
+  for (int i = 0; i < TT; ++i) acc[i] = 0.f;
+  for (int h = lane * 8; h < H; h += 256) {
+    float wv[8];
+    load8f(w + h, wv);
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
-      const float v = warp_sum(acc[tt]);
-      if (lane == 0 && t0 + tt < T) logits[(size_t)(t0 + tt) * E + e] = v;
+      if (t0 + tt < T) {
+        float xv[8];
+        load8f(x + (size_t)(t0 + tt) * ldx + h, xv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[tt] = fmaf(xv[i], wv[i], acc[tt]);
+      }
     }
   }
+#pragma unroll
+  for (int tt = 0; tt < TT; ++tt) {
+    const float v = warp_sum(acc[tt]);
+    if (lane == 0 && t0 + tt < T) logits[(size_t)(t0 + tt) * E + e] = v;
+  }
 }
+
+constexpr int SCAN = 8;  // route ids a lane reads ahead while scanning
 
 // counts[e] = number of routes that chose expert e.  One warp per expert.
 __global__ void moe_count_kernel(const int* __restrict__ ids, int* __restrict__ counts, int R, int E) {
@@ -125,10 +137,15 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int* __restrict__ 
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (e >= E) return;
   int c = 0;
-  for (int base = 0; base < R; base += 32) {
-    const int r = base + lane;
-    const bool hit = r < R && ids[r] == e;
-    c += __popc(__ballot_sync(0xffffffffu, hit));
+  for (int base = 0; base < R; base += 32 * SCAN) {
+    int v[SCAN];                      // SCAN independent loads in flight
+#pragma unroll
+    for (int u = 0; u < SCAN; ++u) {
+      const int r = base + 32 * u + lane;
+      v[u] = r < R ? ids[r] : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < SCAN; ++u) c += __popc(__ballot_sync(0xffffffffu, v[u] == e));
   }
   if (lane == 0) counts[e] = c;
 }
@@ -165,16 +182,25 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
     }
   }
   int at = before;
-  for (int base = 0; base < R; base += 32) {
-    const int r = base + lane;
-    const bool hit = r < R && ids[r] == e;
-    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-    if (hit) {
-      const int dst = at + __popc(ballot & ((1u << lane) - 1u));
-      sorted_route[dst] = r;
-      sorted_token[dst] = r / k;
+  for (int base = 0; base < R; base += 32 * SCAN) {
+    int v[SCAN];
+#pragma unroll
+    for (int u = 0; u < SCAN; ++u) {
+      const int r = base + 32 * u + lane;
+      v[u] = r < R ? ids[r] : -1;
     }
-    at += __popc(ballot);
+#pragma unroll
+    for (int u = 0; u < SCAN; ++u) {
+      const bool hit = v[u] == e;
+      const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int r = base + 32 * u + lane;
+        const int dst = at + __popc(ballot & ((1u << lane) - 1u));
+        sorted_route[dst] = r;
+        sorted_token[dst] = r / k;
+      }
+      at += __popc(ballot);
+    }
   }
 }
 
@@ -203,10 +229,11 @@ int ft_router_select(const float* logits, const float* bias, int* ids, float* we
 int ft_router_logits(const void* x, int x_dtype, long long ldx, const float* W, float* logits,
                      int T, int E, int H, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
+  if ((H & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return FT_ERR_SHAPE;
   const int warps = 4;
-  const int blocks = (E + warps - 1) / warps;
+  dim3 grid((E + warps - 1) / warps, (T + 7) / 8);
   FT_DISPATCH(x_dtype, AT,
-              router_logits_kernel<AT><<<blocks, warps * 32, 0, stream>>>((const AT*)x, ldx, W, logits, T, E, H));
+              router_logits_kernel<AT><<<grid, warps * 32, 0, stream>>>((const AT*)x, ldx, W, logits, T, E, H));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

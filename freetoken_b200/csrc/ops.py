@@ -357,6 +357,27 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
              _stream()), "attn_decode")
 
 
+def attn_prefill(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
+                 tile_seg: torch.Tensor, tile_q0: torch.Tensor, seg_q_start: torch.Tensor,
+                 seg_pos0: torch.Tensor, block_table: torch.Tensor, num_heads: int,
+                 num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> None:
+    """Tensor-core causal attention for the query tiles (64 tokens) listed in
+    ``tile_seg`` / ``tile_q0`` (bfloat16; head sizes of :data:`DECODE_HEAD_DIMS`)."""
+    _need(q, "q", torch.bfloat16)
+    _need(out, "out", torch.bfloat16)
+    _need(kv_pages, "kv_pages", torch.bfloat16)
+    if not attn_decode_takes(q, head_dim):
+        raise KernelError(f"attn_prefill: head_dim {head_dim} not in {DECODE_HEAD_DIMS}")
+    for name, t in (("tile_seg", tile_seg), ("tile_q0", tile_q0), ("seg_q_start", seg_q_start),
+                    ("seg_pos0", seg_pos0), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    f = _fn("attention_prefill", "ft_attn_prefill", "p p p p p p p p q q i i i i i i i f")
+    _check(f(_ptr(q), _ptr(out), _ptr(kv_pages), _ptr(tile_seg), _ptr(tile_q0), _ptr(seg_q_start),
+             _ptr(seg_pos0), _ptr(block_table), kv_pages.stride(1), kv_pages.stride(0), num_heads,
+             num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1], int(window or 0),
+             tile_seg.numel(), float(scale), _stream()), "attn_prefill")
+
+
 # ---------------------------------------------------------------- router
 def router_select(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
                   weights: torch.Tensor, k: int, softmax_scoring: bool, renormalize: bool,
@@ -372,8 +393,13 @@ def router_select(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch
              int(renormalize), float(scale), _stream()), "router_select")
 
 
+def router_logits_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.dtype == torch.float32)
+
+
 def router_logits(x: torch.Tensor, w: torch.Tensor, logits: torch.Tensor) -> None:
-    """logits = x @ w^T in float32 for few tokens (one warp per expert row)."""
+    """logits = x @ w^T in float32 for few tokens (a warp per expert row and 8 tokens)."""
     _need(x, "x", contiguous=False)
     _need(w, "w", torch.float32)
     _need(logits, "logits", torch.float32)

@@ -29,7 +29,7 @@ from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage, kv_bytes_per_token
 from ..csrc import build, ops
 from ..models.model import Model
-from ..parts.base import CacheView, Segment, StepContext, Workspace
+from ..parts.base import PREFILL_TILE, CacheView, Segment, StepContext, Workspace
 from ..registry import Architecture, architecture_of, get_architecture, read_model_config
 from ..weights.loader import check_state, load_tensors
 from ..weights.random_init import RandomOptions, random_state
@@ -246,10 +246,13 @@ class Engine:
         cur = 0
         dec_rows = [s.q_start for s in segments if s.n == 1]
         pre_rows = [r for s in segments if s.n > 1 for r in range(s.q_start, s.q_start + s.n)]
+        pf_tiles = [(i, q0) for i, s in enumerate(segments) if s.n > 1
+                    for q0 in range(0, s.n, PREFILL_TILE)]
         for name, size in (("token_ids", T), ("token_pos", T), ("token_seg", T), ("seg_slot", S),
                            ("seg_pos0", S), ("seg_q_start", S + 1), ("seg_kv_len", S),
                            ("logit_rows", N), ("dec_rows", len(dec_rows)),
-                           ("pre_rows", len(pre_rows))):
+                           ("pre_rows", len(pre_rows)), ("pf_tile_seg", len(pf_tiles)),
+                           ("pf_tile_q0", len(pf_tiles))):
             off[name] = cur
             cur = _align4(cur + size)
         for g in range(len(groups)):
@@ -279,6 +282,10 @@ class Engine:
             h[off["dec_rows"]: off["dec_rows"] + len(dec_rows)] = np.asarray(dec_rows, dtype=np.int32)
         if pre_rows:
             h[off["pre_rows"]: off["pre_rows"] + len(pre_rows)] = np.asarray(pre_rows, dtype=np.int32)
+        if pf_tiles:
+            tiles = np.asarray(pf_tiles, dtype=np.int32)
+            h[off["pf_tile_seg"]: off["pf_tile_seg"] + len(pf_tiles)] = tiles[:, 0]
+            h[off["pf_tile_q0"]: off["pf_tile_q0"] + len(pf_tiles)] = tiles[:, 1]
         dev = self._meta_dev
         self._last_meta_ints = cur
         dev[:cur].copy_(host[:cur], non_blocking=True)
@@ -298,6 +305,8 @@ class Engine:
             decode_rows=sec("dec_rows", len(dec_rows)) if mixed else None,
             prefill_rows=sec("pre_rows", len(pre_rows)) if mixed else None,
             num_decode_rows=len(dec_rows), num_prefill_rows=len(pre_rows),
+            prefill_tile_seg=sec("pf_tile_seg", len(pf_tiles)),
+            prefill_tile_q0=sec("pf_tile_q0", len(pf_tiles)), num_prefill_tiles=len(pf_tiles),
             max_decode_kv_len=(width * P if max_q == 1 else
                                max((s.pos0 + 1 for s in segments if s.n == 1), default=0)))
         in_order = N == T and rows == list(range(T))

@@ -94,7 +94,7 @@ class PagedAttention(Mixer):
             self.w_knorm = tensors[self.n_knorm]
 
     def libraries(self, dtype) -> List[str]:
-        fast = ["attention_decode"] if dtype == torch.bfloat16 else []
+        fast = ["attention_decode", "attention_prefill"] if dtype == torch.bfloat16 else []
         return ["elementwise", "attention_simt"] + fast + linear.libraries(dtype)
 
     # ---- forward ----------------------------------------------------------------
@@ -120,13 +120,15 @@ class PagedAttention(Mixer):
         longer segments to the prefill kernel; sizes those refuse (and the
         float32 path) go to the generic kernel.  ``decode_rows`` /
         ``prefill_rows`` are only set when a step has both kinds."""
-        rest = None          # rows left for the generic kernel; None = all rows
-        if ctx.num_decode_rows > 0 and ops.attn_decode_takes(q, self.d):
-            ops.attn_decode(q, o, cache.kv_pages, ctx.decode_rows, ctx.num_decode_rows,
-                            ctx.token_pos, ctx.token_seg, table, self.nq, self.nkv, self.d,
-                            self.scale, self.window, ctx.max_decode_kv_len, ctx.workspace)
-            if ctx.num_prefill_rows == 0:
-                return
-            rest = ctx.prefill_rows
+        if ops.attn_decode_takes(q, self.d):
+            if ctx.num_decode_rows > 0:
+                ops.attn_decode(q, o, cache.kv_pages, ctx.decode_rows, ctx.num_decode_rows,
+                                ctx.token_pos, ctx.token_seg, table, self.nq, self.nkv, self.d,
+                                self.scale, self.window, ctx.max_decode_kv_len, ctx.workspace)
+            if ctx.num_prefill_tiles > 0:
+                ops.attn_prefill(q, o, cache.kv_pages, ctx.prefill_tile_seg, ctx.prefill_tile_q0,
+                                 ctx.seg_q_start, ctx.seg_pos0, table, self.nq, self.nkv, self.d,
+                                 self.scale, self.window)
+            return
         ops.attn_paged_simt(q, o, cache.kv_pages, ctx.token_pos, ctx.token_seg, table,
-                            self.nq, self.nkv, self.d, self.scale, self.window, rows=rest)
+                            self.nq, self.nkv, self.d, self.scale, self.window)

@@ -80,6 +80,9 @@ class Workspace:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 
 
+PREFILL_TILE = 64   # query tokens per tile of the prefill attention kernel
+
+
 @dataclass
 class StepContext:
     """Everything a part may read about the step it runs in."""
@@ -110,6 +113,11 @@ class StepContext:
     num_decode_rows: int = 0
     num_prefill_rows: int = 0
     max_decode_kv_len: int = 0
+    # query tiles (PREFILL_TILE tokens) of the longer segments: segment index
+    # and first token inside the segment, device int32
+    prefill_tile_seg: Optional[torch.Tensor] = None
+    prefill_tile_q0: Optional[torch.Tensor] = None
+    num_prefill_tiles: int = 0
     # when set, parts may leave measurements here (the benchmark counts the
     # experts a step touched); never set on the serving path
     probe: Optional[Dict[str, Any]] = None

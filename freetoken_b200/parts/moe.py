@@ -95,7 +95,7 @@ class RoutedExperts(FeedForward):
         T = x.shape[0]
         ws = ctx.workspace
         logits = ws.get("moe.logits", (T, self.E), torch.float32)
-        if ctx.dtype == torch.bfloat16 and T <= ROUTER_SMALL_T:
+        if ctx.dtype == torch.bfloat16 and T <= ROUTER_SMALL_T and ops.router_logits_takes(x, self.w_router):
             ops.router_logits(x, self.w_router, logits)
         else:
             ops.gemm_rows(x, self.w_router, logits)

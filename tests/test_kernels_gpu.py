@@ -432,10 +432,38 @@ def test_attn_decode(nq, nkv, d, P, positions, window, standout):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T,E,H", [(1, 4, 64), (8, 256, 3072), (33, 37, 100)])
+@pytest.mark.parametrize("T,E,H", [(1, 4, 64), (8, 256, 3072), (33, 37, 104)])
 def test_router_logits(dtype, T, E, H):
     x = rnd(T, H, dtype=DT[dtype], seed=1)
     w = rnd(E, H, seed=2, scale=0.05)
     out = torch.empty(T, E, device=DEV)
     ops().router_logits(x, w, out)
     assert torch.allclose(out, x.float() @ w.t(), atol=1e-4, rtol=1e-5)
+
+
+# ----------------------------------------------------- prefill attention (mma)
+PREFILL_CASES = [
+    # nq, nkv, d, P, segments (pos0, n), window, standout
+    (6, 1, 128, 64, [(0, 70)], None, None),
+    (4, 2, 64, 16, [(0, 3), (17, 2), (100, 130)], None, (2, 7)),   # far key, prefix in the cache
+    (12, 2, 32, 4, [(5, 64), (0, 65)], None, None),                 # tile edges: 64 and 65 tokens
+    (4, 4, 64, 8, [(30, 90)], 20, None),                            # window shorter than a tile
+    (8, 2, 128, 64, [(1000, 2), (0, 2)], None, (0, 500)),           # two-token portions
+]
+
+
+@pytest.mark.parametrize("nq,nkv,d,P,lens,window,standout", PREFILL_CASES)
+def test_attn_prefill(nq, nkv, d, P, lens, window, standout):
+    o = ops()
+    q, kv, pos, seg, table = _paged_case("bfloat16", nq, nkv, d, P, lens, window, standout=standout)
+    out = torch.zeros_like(q)
+    scale = d ** -0.5
+    starts = [0]
+    for _, n in lens:
+        starts.append(starts[-1] + n)
+    tiles = [(s, q0) for s, (_, n) in enumerate(lens) for q0 in range(0, n, 64)]
+    dev = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
+    o.attn_prefill(q, out, kv, dev([t[0] for t in tiles]), dev([t[1] for t in tiles]), dev(starts),
+                   dev([p for p, _ in lens]), table, nq, nkv, d, scale, window)
+    want = _attn_ref(q, kv, pos, seg, table, nq, nkv, d, P, scale, window)
+    assert torch.allclose(out.float().cpu(), want, **TOL["bfloat16"])
