@@ -42,6 +42,7 @@ LIBRARIES: Dict[str, str] = {
     "skinny_gemm": "skinny_gemm.cu",
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
+    "moe_gemm_tc": "moe_gemm_tc.cu",
 }
 HEADERS: List[str] = ["common.cuh", "mma_utils.cuh"]
 EXTRA_LINK: Dict[str, List[str]] = {}

@@ -1,0 +1,378 @@
+// Grouped expert GEMM on the 5th-generation tensor cores (tcgen05 + TMEM),
+// operands staged in shared memory by TMA.
+//
+// For every expert e that has rows (sorted routes off[e]..off[e+1]) and every
+// tile of 128 weight rows:   D[128 weight rows, N tokens] = W_e tile * X^T
+// The WEIGHTS are the M operand of the MMA (always a full 128-row tile, whatever
+// the load of the expert), the expert's TOKENS are the N operand (N = 16..128
+// per tile), both K-major, so neither needs a transpose and an expert with few
+// tokens wastes little of the tensor core.  Accumulation is float32 in TMEM.
+//
+//   warp 0     TMA producer: per 64-wide k-block one weight box (two with GLU:
+//              gate rows and up rows) and one token box into a ring of stages,
+//              completion on the stage's "full" mbarrier
+//   warp 1     allocates TMEM; one thread issues tcgen05.mma (M=128, N, K=16)
+//              four per k-block, then tcgen05.commit to the stage's "empty"
+//              mbarrier, and after the last k-block to the "accumulator" one
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (a thread owns one weight
+//              row = one TMEM lane), GLU: act(gate)*up; down: * route weight in
+//              float32; round; store transposed into [token, feature] rows
+//
+// Every mbarrier wait is bounded (about two seconds): on expiry the CTA writes
+// a code into `status`, stops issuing work, frees its TMEM and returns.
+//
+// Reference counterpart: python/freetoken/kernel/triton/fused_moe.py:156-302
+// (tl.dot grouped GEMM over block-padded sorted tokens),
+// python/freetoken/kernel/triton/activation.py:96-107 (activation as its own
+// kernel), weight multiply at fused_moe.py:292-296.
+#include <cuda.h>
+
+#include <cstring>
+
+#include "common.cuh"
+
+namespace ft {
+
+constexpr int TC_BM = 128;         // weight rows per tile (UMMA M)
+constexpr int TC_BK = 64;          // k-block: 64 bf16 = 128 bytes = one swizzle row
+constexpr int TC_MAXN = 128;       // most tokens per tile (UMMA N)
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;     // 16 KB
+constexpr int TC_B_BYTES = TC_MAXN * TC_BK * 2;   // 16 KB reserved per stage
+
+struct TcArgs {
+  void* C;
+  const int* group_offsets;   // [G+1]
+  const int* active;          // [G+1]: experts with rows, then their number
+  const int* c_rows;          // sorted row -> output row, or nullptr
+  const float* row_scale;     // by output row, or nullptr
+  int* status;                // 0 = fine; otherwise the first failure code
+  long long ldc;
+  int n_out;                  // output features (weight rows; with GLU: rows of each half)
+  int K, G, ntok;
+  int act;
+  float act_alpha, act_limit;
+};
+
+// ------------------------------------------------------------------ PTX
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false after ~2 s or once another role has given up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* gave_up) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long start = global_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*gave_up) return false;
+    if (global_ns() - start > 2000000000ull) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                       unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(unsigned taddr, unsigned (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in the 128-byte swizzle TMA writes: rows of 128 bytes,
+// 8-row groups 1024 bytes apart.  start address, LBO (unused) = 1, SBO = 1024,
+// descriptor version 1 (sm_100), layout 2 = SWIZZLE_128B.
+__device__ __forceinline__ unsigned long long sw128_desc(unsigned smem_addr) {
+  return (unsigned long long)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+
+__device__ __forceinline__ float tc_glu(float g, float u, int act, float alpha, float limit) {
+  if (act == 0) return (g / (1.f + __expf(-g))) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return (g / (1.f + __expf(-alpha * g))) * (u + 1.f);
+}
+
+template <bool GLU>
+__global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
+                                                          const __grid_constant__ CUtensorMap tm_x,
+                                                          TcArgs a) {
+  constexpr int STAGES = GLU ? 4 : 6;
+  constexpr int STAGE_BYTES = (GLU ? 2 : 1) * TC_A_BYTES + TC_B_BYTES;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], accum_bar;
+  __shared__ unsigned tmem_slot;
+  __shared__ int tile_info[3];       // expert, first row, end row of the expert
+  __shared__ volatile int gave_up;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    int e = -1, row0 = 0, row_end = 0;
+    int y = blockIdx.y;
+    const int busy = a.active[a.G];
+    for (int j = 0; j < busy; ++j) {
+      const int ex = a.active[j];
+      const int begin = a.group_offsets[ex], end = a.group_offsets[ex + 1];
+      const int nt = (end - begin + a.ntok - 1) / a.ntok;
+      if (y < nt) { e = ex; row0 = begin + y * a.ntok; row_end = end; break; }
+      y -= nt;
+    }
+    tile_info[0] = e; tile_info[1] = row0; tile_info[2] = row_end;
+    gave_up = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int e = tile_info[0], row0 = tile_info[1], row_end = tile_info[2];
+  if (e < 0) return;
+  const int n0 = blockIdx.x * TC_BM;
+  const int ntok = a.ntok;
+  const unsigned tmem_cols = (GLU ? 2 * ntok : ntok) <= 32 ? 32u : ((GLU ? 2 * ntok : ntok) <= 64 ? 64u :
+                             ((GLU ? 2 * ntok : ntok) <= 128 ? 128u : 256u));
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = tmem_slot;
+  const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const unsigned tx = (GLU ? 2 : 1) * TC_A_BYTES + (unsigned)ntok * TC_BK * 2;
+      int issued = 0;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        const int s = kb % STAGES;
+        const unsigned ph = (unsigned)(kb / STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, &gave_up)) {
+          atomicCAS(a.status, 0, 1);
+          gave_up = 1;
+          break;
+        }
+        unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], tx);
+        tma_load_3d(st, &tm_w, kb * TC_BK, n0, e, &full_bar[s]);
+        if (GLU) tma_load_3d(st + TC_A_BYTES, &tm_w, kb * TC_BK, a.n_out + n0, e, &full_bar[s]);
+        tma_load_2d(st + (GLU ? 2 : 1) * TC_A_BYTES, &tm_x, kb * TC_BK, row0, &full_bar[s]);
+        issued = kb + 1;
+      }
+      if (gave_up) {
+        // let copies already in flight land before the CTA (and its shared memory) goes away
+        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+          const unsigned long long start = global_ns();
+          while (!mbar_try(&full_bar[kb % STAGES], (unsigned)(kb / STAGES) & 1u) &&
+                 global_ns() - start < 100000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: D f32, A/B bf16, both K-major, N, M = 128
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(ntok >> 3) << 17) |
+                             ((unsigned)(TC_BM >> 4) << 24);
+      bool ok = true;
+      for (int kb = 0; kb < kblocks && ok; ++kb) {
+        const int s = kb % STAGES;
+        const unsigned ph = (unsigned)(kb / STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, &gave_up)) {
+          atomicCAS(a.status, 0, 2);
+          gave_up = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const unsigned st = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+        const unsigned sb = st + (GLU ? 2 : 1) * TC_A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < TC_BK / 16; ++kk) {
+          const unsigned acc = (kb | kk) != 0;
+          const unsigned long long bdesc = sw128_desc(sb + kk * 32);
+          tc_mma(tmem_base, sw128_desc(st + kk * 32), bdesc, idesc, acc);
+          if (GLU) tc_mma(tmem_base + ntok, sw128_desc(st + TC_A_BYTES + kk * 32), bdesc, idesc, acc);
+        }
+        tc_commit(&empty_bar[s]);
+      }
+      if (ok) tc_commit(&accum_bar);
+    }
+  } else {
+    // epilogue: TMEM lane = weight row; this warp may touch lanes 32*(warp%4) .. +31
+    const int lane_base = (warp & 3) * 32;
+    const int n = n0 + lane_base + lane;
+    bool ok = mbar_wait(&accum_bar, 0u, &gave_up);
+    if (!ok && lane == 0) { atomicCAS(a.status, 0, 3); gave_up = 1; }
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* C = (__nv_bfloat16*)a.C;
+      for (int c0 = 0; c0 < ntok; c0 += 16) {
+        unsigned g[16], u[16];
+        const unsigned taddr = tmem_base + ((unsigned)lane_base << 16) + (unsigned)c0;
+        tc_ld16(taddr, g);
+        if (GLU) tc_ld16(taddr + ntok, u);
+        tc_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int row = row0 + c0 + c;
+          if (row < row_end && n < a.n_out) {
+            float v = __uint_as_float(g[c]);
+            if (GLU) v = tc_glu(v, __uint_as_float(u[c]), a.act, a.act_alpha, a.act_limit);
+            const int crow = a.c_rows ? a.c_rows[row] : row;
+            if (a.row_scale) v *= a.row_scale[crow];
+            C[(size_t)crow * a.ldc + n] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+}  // namespace ft
+
+using namespace ft;
+
+extern "C" {
+
+// Tensor map over bfloat16 [groups, rows, K] (groups = 1 for a plain matrix)
+// with boxes of [box_rows, 64] in the 128-byte swizzle.  `out` receives 128 bytes.
+int ft_tc_make_map(void* out, const void* base, long long groups, long long rows, long long K,
+                   long long row_stride, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -201;
+  if ((K & 7) || (row_stride & 7) || ((uintptr_t)base & 15) || box_rows < 1 || box_rows > 256) return FT_ERR_SHAPE;
+  CUtensorMap map;
+  CUresult rc;
+  if (groups > 1) {
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)groups};
+    cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)rows * (cuuint64_t)row_stride * 2};
+    cuuint32_t box[3] = {TC_BK, (cuuint32_t)box_rows, 1};
+    cuuint32_t es[3] = {1, 1, 1};
+    rc = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)base, dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t es[2] = {1, 1};
+    rc = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (rc != CUDA_SUCCESS) return -202;
+  memcpy(out, &map, sizeof(map));
+  return FT_OK;
+}
+
+// C rows (bfloat16) for the sorted rows of every busy expert.  map_w: 3-D map of
+// the expert weights (box 128 rows); map_x: 2-D map of the sorted token rows
+// (box `ntok` rows).  rows_bound: most sorted rows there can be.
+int ft_moe_gemm_tc(const void* map_w, const void* map_x, void* C, long long ldc,
+                   const int* group_offsets, const int* active, const int* c_rows,
+                   const float* row_scale, int* status, int rows_bound, int n_out, int K, int G,
+                   int ntok, int glu, int act, float act_alpha, float act_limit,
+                   cudaStream_t stream) {
+  if (rows_bound <= 0 || n_out <= 0) return FT_OK;
+  if (ntok < 16 || ntok > TC_MAXN || (ntok & 15) || (K & 7) || G <= 0) return FT_ERR_SHAPE;
+  CUtensorMap mw, mx;
+  memcpy(&mw, map_w, sizeof(mw));
+  memcpy(&mx, map_x, sizeof(mx));
+  TcArgs a{C, group_offsets, active, c_rows, row_scale, status, ldc, n_out, K, G, ntok, act, act_alpha, act_limit};
+  const int tiles_y = (rows_bound + ntok - 1) / ntok + (G < rows_bound ? G : rows_bound);
+  dim3 grid((n_out + TC_BM - 1) / TC_BM, tiles_y);
+  if (glu) {
+    const size_t smem = 4 * (2 * TC_A_BYTES + TC_B_BYTES) + 1024;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    moe_gemm_tc_kernel<true><<<grid, 192, smem, stream>>>(mw, mx, a);
+  } else {
+    const size_t smem = 6 * (TC_A_BYTES + TC_B_BYTES) + 1024;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    moe_gemm_tc_kernel<false><<<grid, 192, smem, stream>>>(mw, mx, a);
+  }
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+}  // extern "C"

@@ -275,6 +275,89 @@ def skinny_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
              rows_per_pass, _stream()), "skinny_gemm")
 
 
+# ------------------------------------------------ grouped GEMM on tcgen05
+_TC_MAPS = {}
+_TC_STATUS = {}
+
+
+def tc_status(device) -> torch.Tensor:
+    """The device word in which a tcgen05 kernel records a wait that ran out."""
+    idx = torch.device(device).index or 0
+    if idx not in _TC_STATUS:
+        _TC_STATUS[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _TC_STATUS[idx]
+
+
+def check_tc_status(device) -> None:
+    """Raise if a tensor-core kernel gave up a wait since the last check (synchronises)."""
+    idx = torch.device(device).index or 0
+    if idx in _TC_STATUS:
+        code_ = int(_TC_STATUS[idx].item())
+        if code_:
+            _TC_STATUS[idx].zero_()
+            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code_, "a role")
+            raise KernelError(f"moe_gemm_tc: {role} waited on a barrier for over two seconds and gave up")
+
+
+def _tc_map(t: torch.Tensor, rows: int, K: int, row_stride: int, groups: int, box_rows: int):
+    key = (t.data_ptr(), rows, K, row_stride, groups, box_rows)
+    m = _TC_MAPS.get(key)
+    if m is None:
+        if len(_TC_MAPS) > 4096:
+            _TC_MAPS.clear()
+        m = ctypes.create_string_buffer(128)
+        f = getattr(build.load("moe_gemm_tc"), "ft_tc_make_map")
+        f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_longlong,
+                      ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int]
+        f.restype = ctypes.c_int
+        rc = f(ctypes.cast(m, ctypes.c_void_p), t.data_ptr(), groups, rows, K, row_stride, box_rows)
+        if rc != 0:
+            raise KernelError(f"moe_gemm_tc: cannot build a tensor map (code {rc})")
+        _TC_MAPS[key] = m
+    return m
+
+
+def moe_gemm_tc_takes(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool:
+    K = w.shape[-1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and c.dtype == torch.bfloat16
+            and w.dim() == 3 and w.is_contiguous() and K % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and c.stride(1) == 1)
+
+
+def tc_tokens_per_tile(rows: int, groups: int) -> int:
+    """Tokens per MMA tile for ``rows`` sorted rows over ``groups`` experts."""
+    avg = -(-rows // max(1, groups))
+    return min(128, max(16, -(-avg // 16) * 16))
+
+
+def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offsets: torch.Tensor,
+                active: torch.Tensor, c_rows: Optional[torch.Tensor] = None,
+                row_scale: Optional[torch.Tensor] = None, rows: int, glu: bool = False,
+                act: str = "silu", act_alpha: float = 1.702, act_limit: float = 7.0,
+                tokens_per_tile: Optional[int] = None) -> None:
+    """Grouped expert GEMM on tcgen05/TMEM fed by TMA.  ``x`` holds the sorted
+    rows ``[>= rows, K]`` (already gathered), ``w`` is ``[G, N_w, K]``; same
+    output conventions as :func:`gemm_rows`."""
+    if not moe_gemm_tc_takes(x, w, c):
+        raise KernelError("moe_gemm_tc: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
+    G, NW, K = w.shape
+    N = NW // 2 if glu else NW
+    if x.shape[1] != K or c.shape[1] != N:
+        raise KernelError("moe_gemm_tc: shapes do not match")
+    for name, t in (("group_offsets", group_offsets), ("active", active)):
+        _need(t, name, torch.int32)
+    ntok = tokens_per_tile or tc_tokens_per_tile(rows, G)
+    map_w = _tc_map(w, NW, K, K, G, 128)
+    map_x = _tc_map(x, x.shape[0], K, x.stride(0), 1, ntok)
+    status = tc_status(x.device)
+    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p i i i i i i i f f")
+    _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(map_x, ctypes.c_void_p), _ptr(c),
+             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(c_rows), _ptr(row_scale),
+             _ptr(status), rows, N, K, G, ntok, int(glu), 0 if act == "silu" else 1,
+             float(act_alpha), float(act_limit), _stream()), "moe_gemm_tc")
+
+
 def pass_rows(rows: int) -> int:
     """Tokens per pass of the skinny kernel for ``rows`` rows (per group)."""
     return 8 if rows <= 8 else (16 if rows <= 16 else 32)

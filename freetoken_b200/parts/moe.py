@@ -26,6 +26,10 @@ from ..weights.spec import Cat, Init, Name, Stack, TensorSpec
 from .base import FeedForward, StepContext, register_feed_forward
 
 
+# Above this many rows per expert (on average) the experts run on the tcgen05
+# grouped GEMM; below it the weight-streaming kernel reads each expert once.
+TC_MIN_ROWS_PER_EXPERT = 8
+
 # Up to this many tokens the router's logits come from the one-warp-per-expert
 # kernel; above it from the tiled float32 product.
 ROUTER_SMALL_T = 64
@@ -87,7 +91,7 @@ class RoutedExperts(FeedForward):
 
     def libraries(self, dtype) -> List[str]:
         libs = ["gemm_simt", "moe_route", "elementwise"]
-        return libs + (["skinny_gemm"] if dtype == torch.bfloat16 else [])
+        return libs + (["skinny_gemm", "moe_gemm_tc"] if dtype == torch.bfloat16 else [])
 
     # ---- forward ----------------------------------------------------------------
     def route(self, ctx: StepContext, x: torch.Tensor):
@@ -130,6 +134,17 @@ class RoutedExperts(FeedForward):
         return parts.view(T, self.k, self.hidden)
 
     def experts(self, ctx, x, mid, parts, offsets, active, sorted_route, sorted_token, route_weight, R):
+        if ctx.dtype == torch.bfloat16 and R > TC_MIN_ROWS_PER_EXPERT * self.E \
+                and ops.moe_gemm_tc_takes(x, self.w_gate_up, mid) \
+                and ops.moe_gemm_tc_takes(mid, self.w_down, parts):
+            # many rows per expert: tcgen05 grouped GEMM over the gathered rows
+            xs = ctx.workspace.get("moe.sorted_x", (R, self.hidden), ctx.dtype)
+            ops.gather_rows(x, sorted_token, xs)
+            ops.moe_gemm_tc(xs, self.w_gate_up, mid, group_offsets=offsets, active=active, rows=R,
+                            glu=True, act=self.act, act_alpha=self.act_alpha, act_limit=self.act_limit)
+            ops.moe_gemm_tc(mid, self.w_down, parts, group_offsets=offsets, active=active,
+                            c_rows=sorted_route, row_scale=route_weight, rows=R)
+            return
         if ctx.dtype == torch.bfloat16 and ops.skinny_gemm_takes(x, self.w_gate_up, mid) \
                 and ops.skinny_gemm_takes(mid, self.w_down, parts):
             per_pass = ops.pass_rows(-(-R // self.E))

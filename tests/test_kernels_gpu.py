@@ -180,9 +180,10 @@ def _grouped_case(E, k, T, seed=0):
     return ids.to(DEV), order.to(DEV), (order // k).to(torch.int32).to(DEV), offsets.to(DEV)
 
 
-@pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "skinny"])
+@pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "skinny", "tc"])
 @pytest.mark.parametrize("E,k,T,H,I,act", [(4, 2, 5, 64, 32, "silu"), (8, 3, 19, 96, 48, "swigluoai"),
-                                           (16, 4, 150, 128, 80, "silu"), (3, 1, 40, 40, 24, "silu")])
+                                           (16, 4, 150, 128, 80, "silu"), (3, 1, 40, 40, 24, "silu"),
+                                           (8, 2, 700, 264, 200, "silu")])
 def test_expert_gemms(kernel, E, k, T, H, I, act):
     """gate_up + GLU, then down with the route weight, against a per-route loop."""
     o = ops()
@@ -195,11 +196,19 @@ def test_expert_gemms(kernel, E, k, T, H, I, act):
     R = T * k
     mid = torch.zeros(R, I, dtype=dt, device=DEV)
     parts = torch.zeros(R, H, dtype=dt, device=DEV)
-    if kernel == "skinny":
+    busy = (offsets[1:] > offsets[:-1]).nonzero().flatten().to(torch.int32)
+    active = torch.cat([busy, torch.zeros(E - busy.numel(), dtype=torch.int32, device=DEV),
+                        torch.tensor([busy.numel()], dtype=torch.int32, device=DEV)])
+    if kernel == "tc":
+        xs = torch.empty(R, H, dtype=dt, device=DEV)
+        o.gather_rows(x, sorted_token, xs)
+        o.moe_gemm_tc(xs, w1, mid, group_offsets=offsets, active=active, rows=R, glu=True, act=act)
+        o.moe_gemm_tc(mid, w2, parts, group_offsets=offsets, active=active, c_rows=sorted_route,
+                      row_scale=rw, rows=R)
+        torch.cuda.synchronize()
+        o.check_tc_status(DEV)
+    elif kernel == "skinny":
         per = o.pass_rows(-(-R // E))
-        busy = (offsets[1:] > offsets[:-1]).nonzero().flatten().to(torch.int32)
-        active = torch.cat([busy, torch.zeros(E - busy.numel(), dtype=torch.int32, device=DEV),
-                            torch.tensor([busy.numel()], dtype=torch.int32, device=DEV)])
         o.skinny_gemm(x, w1, mid, group_offsets=offsets, active=active, a_rows=sorted_token,
                       rows=R, glu=True, act=act, rows_per_pass=per)
         o.skinny_gemm(mid, w2, parts, group_offsets=offsets, c_rows=sorted_route, row_scale=rw,
@@ -209,14 +218,19 @@ def test_expert_gemms(kernel, E, k, T, H, I, act):
         o.gemm_rows(mid, w2, parts, group_offsets=offsets, c_rows=sorted_route, row_scale=rw, rows=R)
     tol = TOL["float32" if kernel == "simt_f32" else "bfloat16"]
     flat = ids.view(-1).long()
-    for r in range(R):
-        e, t = int(flat[r]), r // k
-        gu = w1[e].float() @ x[t].float()
-        m = _glu(gu[:I], gu[I:], act)
-        spos = int((sorted_route == r).nonzero()[0])
-        assert torch.allclose(mid[spos].float(), m, atol=tol["atol"], rtol=tol["rtol"]), (r, "mid")
-        y = (w2[e].float() @ mid[spos].float()) * rw[r]
-        assert torch.allclose(parts[r].float(), y, atol=tol["atol"], rtol=tol["rtol"]), (r, "down")
+    # per-route reference, vectorised per expert
+    inv = torch.empty(R, dtype=torch.long, device=DEV)
+    inv[sorted_route.long()] = torch.arange(R, device=DEV)
+    for e in range(E):
+        rs = (flat == e).nonzero().flatten()
+        if rs.numel() == 0:
+            continue
+        gu = x[rs // k].float() @ w1[e].float().t()
+        m = _glu(gu[:, :I], gu[:, I:], act)
+        got_mid = mid[inv[rs]].float()
+        assert torch.allclose(got_mid, m, atol=tol["atol"], rtol=tol["rtol"]), (e, "mid")
+        y = (got_mid @ w2[e].float().t()) * rw[rs][:, None]
+        assert torch.allclose(parts[rs].float(), y, atol=tol["atol"], rtol=tol["rtol"]), (e, "down")
 
 
 @pytest.mark.parametrize("ct", ["bfloat16", "float32"])
