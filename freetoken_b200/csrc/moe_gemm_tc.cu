@@ -17,6 +17,8 @@
 //   warps 2-5  epilogue: tcgen05.ld the accumulator (a thread owns one weight
 //              row = one TMEM lane), GLU: act(gate)*up; down: * route weight in
 //              float32; round; store transposed into [token, feature] rows
+// The kernel is persistent (one CTA per SM) and the accumulator has two TMEM
+// buffers, so a tile's epilogue runs while the next tile's k-blocks stream in.
 //
 // Every mbarrier wait is bounded (about two seconds): on expiry the CTA writes
 // a code into `status`, stops issuing work, frees its TMEM and returns.
@@ -43,12 +45,14 @@ struct TcArgs {
   void* C;
   const int* group_offsets;   // [G+1]
   const int* active;          // [G+1]: experts with rows, then their number
+  const int* tile_expert;     // [tiles_bound]: expert of each (expert, token tile), -1 past the end
+  const int* tile_row0;       // [tiles_bound]: first sorted row of the tile
   const int* c_rows;          // sorted row -> output row, or nullptr
   const float* row_scale;     // by output row, or nullptr
   int* status;                // 0 = fine; otherwise the first failure code
   long long ldc;
   int n_out;                  // output features (weight rows; with GLU: rows of each half)
-  int K, G, ntok;
+  int K, G, ntok, tiles_y;
   int act;
   float act_alpha, act_limit;
 };
@@ -139,6 +143,15 @@ __device__ __forceinline__ float tc_glu(float g, float u, int act, float alpha, 
   return (g / (1.f + __expf(-alpha * g))) * (u + 1.f);
 }
 
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent: one CTA per SM walks the tiles t = blockIdx.x, + gridDim.x, ...
+// of the (token tile, weight tile) space, weight tile fastest, so CTAs that run
+// side by side share an expert.  The TMA ring never drains between tiles and the
+// accumulator is double-buffered in TMEM, so the epilogue of one tile runs under
+// the main loop of the next.
 template <bool GLU>
 __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                           const __grid_constant__ CUtensorMap tm_x,
@@ -147,36 +160,22 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
   constexpr int STAGE_BYTES = (GLU ? 2 : 1) * TC_A_BYTES + TC_B_BYTES;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], accum_bar;
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
+  __shared__ __align__(8) unsigned long long acc_full[2], acc_empty[2];
   __shared__ unsigned tmem_slot;
-  __shared__ int tile_info[3];       // expert, first row, end row of the expert
   __shared__ volatile int gave_up;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ntok = a.ntok;
+  const int acc_cols = GLU ? 2 * ntok : ntok;             // columns of one accumulator buffer
+  const unsigned tmem_cols = 2 * acc_cols <= 32 ? 32u : (2 * acc_cols <= 64 ? 64u :
+                             (2 * acc_cols <= 128 ? 128u : (2 * acc_cols <= 256 ? 256u : 512u)));
   if (threadIdx.x == 0) {
-    int e = -1, row0 = 0, row_end = 0;
-    int y = blockIdx.y;
-    const int busy = a.active[a.G];
-    for (int j = 0; j < busy; ++j) {
-      const int ex = a.active[j];
-      const int begin = a.group_offsets[ex], end = a.group_offsets[ex + 1];
-      const int nt = (end - begin + a.ntok - 1) / a.ntok;
-      if (y < nt) { e = ex; row0 = begin + y * a.ntok; row_end = end; break; }
-      y -= nt;
-    }
-    tile_info[0] = e; tile_info[1] = row0; tile_info[2] = row_end;
     gave_up = 0;
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(&accum_bar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
-  const int e = tile_info[0], row0 = tile_info[1], row_end = tile_info[2];
-  if (e < 0) return;
-  const int n0 = blockIdx.x * TC_BM;
-  const int ntok = a.ntok;
-  const unsigned tmem_cols = (GLU ? 2 * ntok : ntok) <= 32 ? 32u : ((GLU ? 2 * ntok : ntok) <= 64 ? 64u :
-                             ((GLU ? 2 * ntok : ntok) <= 128 ? 128u : 256u));
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
                  "r"(tmem_cols) : "memory");
@@ -187,29 +186,38 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
   tc_fence_after();
   const unsigned tmem_base = tmem_slot;
   const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+  const int wtiles = (a.n_out + TC_BM - 1) / TC_BM;
+  const int total = a.tiles_y * wtiles;
 
   if (warp == 0) {
     if (lane == 0) {
       const unsigned tx = (GLU ? 2 : 1) * TC_A_BYTES + (unsigned)ntok * TC_BK * 2;
-      int issued = 0;
-      for (int kb = 0; kb < kblocks; ++kb) {
-        const int s = kb % STAGES;
-        const unsigned ph = (unsigned)(kb / STAGES) & 1u;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u, &gave_up)) {
-          atomicCAS(a.status, 0, 1);
-          gave_up = 1;
-          break;
+      long long issued = 0;           // k-blocks issued so far, over all tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const int y = t / wtiles, n0 = (t % wtiles) * TC_BM;
+        const int e = a.tile_expert[y];
+        if (e < 0) continue;
+        const int row0 = a.tile_row0[y];
+        for (int kb = 0; kb < kblocks; ++kb, ++issued) {
+          const int s = (int)(issued % STAGES);
+          const unsigned ph = (unsigned)(issued / STAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, &gave_up)) {
+            atomicCAS(a.status, 0, 1);
+            gave_up = 1;
+            ok = false;
+            break;
+          }
+          unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], tx);
+          tma_load_3d(st, &tm_w, kb * TC_BK, n0, e, &full_bar[s]);
+          if (GLU) tma_load_3d(st + TC_A_BYTES, &tm_w, kb * TC_BK, a.n_out + n0, e, &full_bar[s]);
+          tma_load_2d(st + (GLU ? 2 : 1) * TC_A_BYTES, &tm_x, kb * TC_BK, row0, &full_bar[s]);
         }
-        unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], tx);
-        tma_load_3d(st, &tm_w, kb * TC_BK, n0, e, &full_bar[s]);
-        if (GLU) tma_load_3d(st + TC_A_BYTES, &tm_w, kb * TC_BK, a.n_out + n0, e, &full_bar[s]);
-        tma_load_2d(st + (GLU ? 2 : 1) * TC_A_BYTES, &tm_x, kb * TC_BK, row0, &full_bar[s]);
-        issued = kb + 1;
       }
       if (gave_up) {
         // let copies already in flight land before the CTA (and its shared memory) goes away
-        for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+        for (long long kb = issued > STAGES ? issued - STAGES : 0; kb < issued; ++kb) {
           const unsigned long long start = global_ns();
           while (!mbar_try(&full_bar[kb % STAGES], (unsigned)(kb / STAGES) & 1u) &&
                  global_ns() - start < 100000000ull) {}
@@ -221,58 +229,89 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
       // instruction descriptor: D f32, A/B bf16, both K-major, N, M = 128
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(ntok >> 3) << 17) |
                              ((unsigned)(TC_BM >> 4) << 24);
+      long long done = 0;             // k-blocks consumed so far
+      int local = 0;                  // tiles this CTA has started
       bool ok = true;
-      for (int kb = 0; kb < kblocks && ok; ++kb) {
-        const int s = kb % STAGES;
-        const unsigned ph = (unsigned)(kb / STAGES) & 1u;
-        if (!mbar_wait(&full_bar[s], ph, &gave_up)) {
-          atomicCAS(a.status, 0, 2);
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        if (a.tile_expert[t / wtiles] < 0) continue;
+        const int b = local & 1;
+        if (!mbar_wait(&acc_empty[b], ((unsigned)(local >> 1) & 1u) ^ 1u, &gave_up)) {
+          atomicCAS(a.status, 0, 4);
           gave_up = 1;
-          ok = false;
           break;
         }
         tc_fence_after();
-        const unsigned st = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-        const unsigned sb = st + (GLU ? 2 : 1) * TC_A_BYTES;
+        const unsigned tmem_d = tmem_base + (unsigned)(b * acc_cols);
+        for (int kb = 0; kb < kblocks; ++kb, ++done) {
+          const int s = (int)(done % STAGES);
+          const unsigned ph = (unsigned)(done / STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, &gave_up)) {
+            atomicCAS(a.status, 0, 2);
+            gave_up = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const unsigned st = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+          const unsigned sb = st + (GLU ? 2 : 1) * TC_A_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < TC_BK / 16; ++kk) {
-          const unsigned acc = (kb | kk) != 0;
-          const unsigned long long bdesc = sw128_desc(sb + kk * 32);
-          tc_mma(tmem_base, sw128_desc(st + kk * 32), bdesc, idesc, acc);
-          if (GLU) tc_mma(tmem_base + ntok, sw128_desc(st + TC_A_BYTES + kk * 32), bdesc, idesc, acc);
+          for (int kk = 0; kk < TC_BK / 16; ++kk) {
+            const unsigned acc = (kb | kk) != 0;
+            const unsigned long long bdesc = sw128_desc(sb + kk * 32);
+            tc_mma(tmem_d, sw128_desc(st + kk * 32), bdesc, idesc, acc);
+            if (GLU) tc_mma(tmem_d + ntok, sw128_desc(st + TC_A_BYTES + kk * 32), bdesc, idesc, acc);
+          }
+          tc_commit(&empty_bar[s]);
         }
-        tc_commit(&empty_bar[s]);
+        if (ok) tc_commit(&acc_full[b]);
+        ++local;
       }
-      if (ok) tc_commit(&accum_bar);
     }
   } else {
     // epilogue: TMEM lane = weight row; this warp may touch lanes 32*(warp%4) .. +31
     const int lane_base = (warp & 3) * 32;
-    const int n = n0 + lane_base + lane;
-    bool ok = mbar_wait(&accum_bar, 0u, &gave_up);
-    if (!ok && lane == 0) { atomicCAS(a.status, 0, 3); gave_up = 1; }
-    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    if (ok) {
+    __nv_bfloat16* C = (__nv_bfloat16*)a.C;
+    int local = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x) {
+      const int y = t / wtiles;
+      const int e = a.tile_expert[y];
+      if (e < 0) continue;
+      const int row0 = a.tile_row0[y], row_end = a.group_offsets[e + 1];
+      const int n = (t % wtiles) * TC_BM + lane_base + lane;
+      const int b = local & 1;
+      bool ok = mbar_wait(&acc_full[b], (unsigned)(local >> 1) & 1u, &gave_up);
+      if (!ok && lane == 0) { atomicCAS(a.status, 0, 3); gave_up = 1; }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
       tc_fence_after();
-      __nv_bfloat16* C = (__nv_bfloat16*)a.C;
+      const unsigned tmem_d = tmem_base + (unsigned)(b * acc_cols) + ((unsigned)lane_base << 16);
       for (int c0 = 0; c0 < ntok; c0 += 16) {
+        // output row and route weight of column c0 + lane (lanes 0..15), handed round by shuffle
+        int my_crow = -1;
+        float my_scale = 1.f;
+        if (lane < 16 && row0 + c0 + lane < row_end) {
+          my_crow = a.c_rows ? a.c_rows[row0 + c0 + lane] : row0 + c0 + lane;
+          if (a.row_scale) my_scale = a.row_scale[my_crow];
+        }
         unsigned g[16], u[16];
-        const unsigned taddr = tmem_base + ((unsigned)lane_base << 16) + (unsigned)c0;
-        tc_ld16(taddr, g);
-        if (GLU) tc_ld16(taddr + ntok, u);
+        tc_ld16(tmem_d + (unsigned)c0, g);
+        if (GLU) tc_ld16(tmem_d + (unsigned)(c0 + ntok), u);
         tc_ld_wait();
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
-          const int row = row0 + c0 + c;
-          if (row < row_end && n < a.n_out) {
+          const int crow = __shfl_sync(0xffffffffu, my_crow, c);
+          const float scale = __shfl_sync(0xffffffffu, my_scale, c);
+          if (crow >= 0 && n < a.n_out) {
             float v = __uint_as_float(g[c]);
             if (GLU) v = tc_glu(v, __uint_as_float(u[c]), a.act, a.act_alpha, a.act_limit);
-            const int crow = a.c_rows ? a.c_rows[row] : row;
-            if (a.row_scale) v *= a.row_scale[crow];
-            C[(size_t)crow * a.ldc + n] = __float2bfloat16_rn(v);
+            C[(size_t)crow * a.ldc + n] = __float2bfloat16_rn(v * scale);
           }
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[b]);
+      ++local;
     }
   }
   tc_fence_before();
@@ -281,6 +320,45 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
+}
+
+// tile_expert[y], tile_row0[y] for every (busy expert, tile of ntok rows), in
+// expert order; entries past the last tile get expert -1.  One block.
+__global__ void moe_tile_map_kernel(const int* __restrict__ group_offsets, const int* __restrict__ active,
+                                    int* __restrict__ tile_expert, int* __restrict__ tile_row0, int G,
+                                    int ntok, int bound) {
+  __shared__ int scan[1024];
+  __shared__ int carry;
+  const int busy = active[G];
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < busy; base += blockDim.x) {
+    const int j = base + threadIdx.x;
+    int e = -1, begin = 0, nt = 0;
+    if (j < busy) {
+      e = active[j];
+      begin = group_offsets[e];
+      nt = (group_offsets[e + 1] - begin + ntok - 1) / ntok;
+    }
+    scan[threadIdx.x] = nt;
+    __syncthreads();
+    // inclusive scan (Hillis-Steele) over the block
+    for (int o = 1; o < (int)blockDim.x; o <<= 1) {
+      const int v = threadIdx.x >= (unsigned)o ? scan[threadIdx.x - o] : 0;
+      __syncthreads();
+      scan[threadIdx.x] += v;
+      __syncthreads();
+    }
+    const int first = carry + scan[threadIdx.x] - nt;
+    for (int i = 0; i < nt && first + i < bound; ++i) {
+      tile_expert[first + i] = e;
+      tile_row0[first + i] = begin + i * ntok;
+    }
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry += scan[threadIdx.x];
+    __syncthreads();
+  }
+  for (int i = carry + threadIdx.x; i < bound; i += blockDim.x) tile_expert[i] = -1;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -339,8 +417,23 @@ int ft_tc_make_map(void* out, const void* base, long long groups, long long rows
 // C rows (bfloat16) for the sorted rows of every busy expert.  map_w: 3-D map of
 // the expert weights (box 128 rows); map_x: 2-D map of the sorted token rows
 // (box `ntok` rows).  rows_bound: most sorted rows there can be.
+// How many (expert, token tile) entries a tile map for `rows_bound` sorted rows needs.
+int ft_tc_tiles_bound(int rows_bound, int G, int ntok) {
+  return (rows_bound + ntok - 1) / ntok + (G < rows_bound ? G : rows_bound);
+}
+
+int ft_moe_tile_map(const int* group_offsets, const int* active, int* tile_expert, int* tile_row0,
+                    int rows_bound, int G, int ntok, cudaStream_t stream) {
+  if (ntok < 1 || G <= 0) return FT_ERR_SHAPE;
+  const int bound = ft_tc_tiles_bound(rows_bound, G, ntok);
+  moe_tile_map_kernel<<<1, 256, 0, stream>>>(group_offsets, active, tile_expert, tile_row0, G, ntok, bound);
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
 int ft_moe_gemm_tc(const void* map_w, const void* map_x, void* C, long long ldc,
-                   const int* group_offsets, const int* active, const int* c_rows,
+                   const int* group_offsets, const int* active, const int* tile_expert,
+                   const int* tile_row0, const int* c_rows,
                    const float* row_scale, int* status, int rows_bound, int n_out, int K, int G,
                    int ntok, int glu, int act, float act_alpha, float act_limit,
                    cudaStream_t stream) {
@@ -349,9 +442,17 @@ int ft_moe_gemm_tc(const void* map_w, const void* map_x, void* C, long long ldc,
   CUtensorMap mw, mx;
   memcpy(&mw, map_w, sizeof(mw));
   memcpy(&mx, map_x, sizeof(mx));
-  TcArgs a{C, group_offsets, active, c_rows, row_scale, status, ldc, n_out, K, G, ntok, act, act_alpha, act_limit};
-  const int tiles_y = (rows_bound + ntok - 1) / ntok + (G < rows_bound ? G : rows_bound);
-  dim3 grid((n_out + TC_BM - 1) / TC_BM, tiles_y);
+  const int tiles_y = ft_tc_tiles_bound(rows_bound, G, ntok);
+  TcArgs a{C, group_offsets, active, tile_expert, tile_row0, c_rows, row_scale, status, ldc, n_out, K, G, ntok,
+           tiles_y, act, act_alpha, act_limit};
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int total = tiles_y * ((n_out + TC_BM - 1) / TC_BM);
+  dim3 grid(total < sms ? total : sms);
   if (glu) {
     const size_t smem = 4 * (2 * TC_A_BYTES + TC_B_BYTES) + 1024;
     static bool configured = false;

@@ -331,14 +331,28 @@ def tc_tokens_per_tile(rows: int, groups: int) -> int:
     return min(128, max(16, -(-avg // 16) * 16))
 
 
+def moe_tile_map(group_offsets: torch.Tensor, active: torch.Tensor, rows: int, groups: int,
+                 tokens_per_tile: int, workspace) -> tuple:
+    """``(tile_expert, tile_row0)`` for the tcgen05 grouped GEMM: one entry per
+    (busy expert, tile of ``tokens_per_tile`` sorted rows)."""
+    bound = -(-rows // tokens_per_tile) + min(groups, rows)
+    tile_expert = workspace.get("moe.tile_expert", (bound,), torch.int32)
+    tile_row0 = workspace.get("moe.tile_row0", (bound,), torch.int32)
+    f = _fn("moe_gemm_tc", "ft_moe_tile_map", "p p p p i i i")
+    _check(f(_ptr(group_offsets), _ptr(active), _ptr(tile_expert), _ptr(tile_row0), rows, groups,
+             tokens_per_tile, _stream()), "moe_tile_map")
+    return tile_expert, tile_row0
+
+
 def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offsets: torch.Tensor,
-                active: torch.Tensor, c_rows: Optional[torch.Tensor] = None,
+                active: torch.Tensor, tile_map: tuple, c_rows: Optional[torch.Tensor] = None,
                 row_scale: Optional[torch.Tensor] = None, rows: int, glu: bool = False,
                 act: str = "silu", act_alpha: float = 1.702, act_limit: float = 7.0,
                 tokens_per_tile: Optional[int] = None) -> None:
     """Grouped expert GEMM on tcgen05/TMEM fed by TMA.  ``x`` holds the sorted
     rows ``[>= rows, K]`` (already gathered), ``w`` is ``[G, N_w, K]``; same
-    output conventions as :func:`gemm_rows`."""
+    output conventions as :func:`gemm_rows`.  ``tile_map`` comes from
+    :func:`moe_tile_map` with the same ``tokens_per_tile``."""
     if not moe_gemm_tc_takes(x, w, c):
         raise KernelError("moe_gemm_tc: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
     G, NW, K = w.shape
@@ -351,9 +365,10 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
     map_w = _tc_map(w, NW, K, K, G, 128)
     map_x = _tc_map(x, x.shape[0], K, x.stride(0), 1, ntok)
     status = tc_status(x.device)
-    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p i i i i i i i f f")
+    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p p p i i i i i i i f f")
     _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(map_x, ctypes.c_void_p), _ptr(c),
-             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(c_rows), _ptr(row_scale),
+             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map[0]), _ptr(tile_map[1]),
+             _ptr(c_rows), _ptr(row_scale),
              _ptr(status), rows, N, K, G, ntok, int(glu), 0 if act == "silu" else 1,
              float(act_alpha), float(act_limit), _stream()), "moe_gemm_tc")
 

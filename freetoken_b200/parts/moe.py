@@ -140,10 +140,14 @@ class RoutedExperts(FeedForward):
             # many rows per expert: tcgen05 grouped GEMM over the gathered rows
             xs = ctx.workspace.get("moe.sorted_x", (R, self.hidden), ctx.dtype)
             ops.gather_rows(x, sorted_token, xs)
-            ops.moe_gemm_tc(xs, self.w_gate_up, mid, group_offsets=offsets, active=active, rows=R,
-                            glu=True, act=self.act, act_alpha=self.act_alpha, act_limit=self.act_limit)
+            ntok = ops.tc_tokens_per_tile(R, self.E)
+            tiles = ops.moe_tile_map(offsets, active, R, self.E, ntok, ctx.workspace)
+            ops.moe_gemm_tc(xs, self.w_gate_up, mid, group_offsets=offsets, active=active,
+                            tile_map=tiles, rows=R, glu=True, act=self.act, act_alpha=self.act_alpha,
+                            act_limit=self.act_limit, tokens_per_tile=ntok)
             ops.moe_gemm_tc(mid, self.w_down, parts, group_offsets=offsets, active=active,
-                            c_rows=sorted_route, row_scale=route_weight, rows=R)
+                            tile_map=tiles, c_rows=sorted_route, row_scale=route_weight, rows=R,
+                            tokens_per_tile=ntok)
             return
         if ctx.dtype == torch.bfloat16 and ops.skinny_gemm_takes(x, self.w_gate_up, mid) \
                 and ops.skinny_gemm_takes(mid, self.w_down, parts):

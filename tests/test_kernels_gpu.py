@@ -202,9 +202,13 @@ def test_expert_gemms(kernel, E, k, T, H, I, act):
     if kernel == "tc":
         xs = torch.empty(R, H, dtype=dt, device=DEV)
         o.gather_rows(x, sorted_token, xs)
-        o.moe_gemm_tc(xs, w1, mid, group_offsets=offsets, active=active, rows=R, glu=True, act=act)
-        o.moe_gemm_tc(mid, w2, parts, group_offsets=offsets, active=active, c_rows=sorted_route,
-                      row_scale=rw, rows=R)
+        from freetoken_b200.parts.base import Workspace
+        ntok = o.tc_tokens_per_tile(R, E)
+        tiles = o.moe_tile_map(offsets, active, R, E, ntok, Workspace(DEV))
+        o.moe_gemm_tc(xs, w1, mid, group_offsets=offsets, active=active, tile_map=tiles, rows=R,
+                      glu=True, act=act, tokens_per_tile=ntok)
+        o.moe_gemm_tc(mid, w2, parts, group_offsets=offsets, active=active, tile_map=tiles,
+                      c_rows=sorted_route, row_scale=rw, rows=R, tokens_per_tile=ntok)
         torch.cuda.synchronize()
         o.check_tc_status(DEV)
     elif kernel == "skinny":
