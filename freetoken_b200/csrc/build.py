@@ -44,7 +44,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_prefill": "attention_prefill.cu",
     "moe_gemm_tc": "moe_gemm_tc.cu",
 }
-HEADERS: List[str] = ["common.cuh", "mma_utils.cuh"]
+HEADERS: List[str] = ["common.cuh", "mma_utils.cuh", "sampling_static.h"]
 EXTRA_LINK: Dict[str, List[str]] = {}
 
 

@@ -163,3 +163,44 @@ extern "C" int ft_sample(const float* logits, const float* temperature, const in
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
+
+// ------------------------------------------------- no-allocation entry point
+// See sampling_static.h.  The scratch lives in the library image; host code
+// only ever sees the symbol as a handle, so the device address is looked up
+// once per device (with that device current) and handed to the kernel.
+#include "sampling_static.h"
+
+static __device__ __align__(256) float ft_sample_static_scratch[FT_SAMPLE_STATIC_FLOATS];
+
+static float* ft_sample_static_address(int* error) {
+  static float* address[64] = {nullptr};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) { *error = (int)e; return nullptr; }
+  if (device < 0 || device >= 64) { *error = FT_ERR_SHAPE; return nullptr; }
+  if (!address[device]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, ft_sample_static_scratch);
+    if (e != cudaSuccess) { *error = (int)e; return nullptr; }
+    address[device] = static_cast<float*>(p);
+  }
+  *error = FT_OK;
+  return address[device];
+}
+
+extern "C" int ft_sample_static(const float* logits, const float* temperature, const int* top_k,
+                                const float* top_p, const float* uniform, int* out, int rows,
+                                int vocab, cudaStream_t stream) {
+  if (rows <= 0) return FT_OK;
+  if (vocab <= 0) return FT_ERR_SHAPE;
+  if ((long long)rows * (long long)vocab > (long long)FT_SAMPLE_STATIC_FLOATS)
+    return FT_ERR_STATIC_TOO_LARGE;
+  if (temperature && !uniform) return FT_ERR_SHAPE;
+  int error = FT_OK;
+  float* scratch = ft_sample_static_address(&error);
+  if (!scratch) return error;
+  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_k, top_p, uniform,
+                                                      out, scratch, vocab);
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
