@@ -1,0 +1,151 @@
+"""Scheduler decisions on the CPU: admission, portions under a token budget,
+mixed steps, finishing and freeing, and what happens when pages run out."""
+
+import random
+
+import pytest
+
+from freetoken_b200.cache import CacheManager, PagedKVNeed
+from freetoken_b200.engine.scheduler import Request, Scheduler
+from freetoken_b200.sampling import SamplingParams
+
+
+def make(num_pages=16, page=4, slots=4, max_seq_len=64, budget=8, eos=()):
+    cache = CacheManager([PagedKVNeed(2, 16, None)], page, num_pages, slots, max_seq_len)
+    return Scheduler(cache, budget, eos), cache
+
+
+def run_step(sched, cache, token_of=lambda r: 7):
+    """What the engine does with a plan: pages, advance, one token per sampling entry."""
+    plan = sched.plan()
+    for e in plan:
+        cache.grow(e.request.id, cache.length(e.request.id) + len(e.tokens))
+    for e in plan:
+        cache.advance(e.request.id, len(e.tokens))
+    done = sched.complete(plan, [token_of(e.request) for e in plan if e.samples])
+    sched.check_integrity()
+    return plan, done
+
+
+def req(rid, n, max_tokens=4, **kw):
+    return Request(rid, list(range(1, n + 1)), SamplingParams(max_tokens=max_tokens, **kw))
+
+
+def test_prompt_is_cut_into_portions_under_the_token_budget():
+    sched, cache = make(budget=8)
+    sched.submit(req("a", 19, max_tokens=2))
+    sizes, samples = [], []
+    while sched.has_work():
+        plan, _ = run_step(sched, cache)
+        sizes.append([len(e.tokens) for e in plan])
+        samples.append([e.samples for e in plan])
+    assert sizes == [[8], [8], [3], [1]]                     # 19 = 8 + 8 + 3, then one decode step
+    assert samples == [[False], [False], [True], [True]]
+    r = sched.finished[0]
+    assert r.output == [7, 7] and r.finish_reason == "length"
+    assert cache.free_pages() == cache.total_pages() and cache.free_slots == 4
+
+
+def test_decode_tokens_ride_beside_prompt_portions():
+    sched, cache = make(budget=8)
+    sched.submit(req("a", 3, max_tokens=6))
+    run_step(sched, cache)                                    # a: whole prompt, first token
+    sched.submit(req("b", 12, max_tokens=2))
+    plan, _ = run_step(sched, cache)
+    assert [(e.request.id, len(e.tokens), e.samples) for e in plan] == [("a", 1, True), ("b", 7, False)]
+    plan, _ = run_step(sched, cache)                          # budget 8 = 1 decode + 5 left of b's prompt
+    assert [(e.request.id, len(e.tokens), e.samples) for e in plan] == [("a", 1, True), ("b", 5, True)]
+    plan, _ = run_step(sched, cache)
+    assert sorted((e.request.id, len(e.tokens)) for e in plan) == [("a", 1), ("b", 1)]
+
+
+def test_several_short_prompts_share_one_step_in_arrival_order():
+    sched, cache = make(budget=10)
+    for rid, n in (("a", 3), ("b", 4), ("c", 6)):
+        sched.submit(req(rid, n))
+    plan, _ = run_step(sched, cache)
+    assert [(e.request.id, len(e.tokens), e.samples) for e in plan] == \
+        [("a", 3, True), ("b", 4, True), ("c", 3, False)]
+
+
+def test_when_pages_run_out_new_requests_wait_and_running_ones_never_starve():
+    # 6 pages of 4 tokens; each request needs ceil((5 + 6) / 4) = 3 pages at worst
+    sched, cache = make(num_pages=6, page=4, slots=4, budget=16)
+    for rid in "abc":
+        sched.submit(req(rid, 5, max_tokens=6))
+    plan, _ = run_step(sched, cache)
+    assert [e.request.id for e in plan] == ["a", "b"]        # c does not fit beside a's and b's worst case
+    assert [r.id for r in sched.pending] == ["c"]
+    steps = 0
+    while sched.has_work():
+        plan, done = run_step(sched, cache)
+        steps += 1
+        assert steps < 50
+        if any(e.request.id == "c" for e in plan):
+            assert {r.id for r in sched.finished} >= {"a"} or {r.id for r in sched.finished} >= {"b"}
+    assert sorted(r.id for r in sched.finished) == ["a", "b", "c"]
+    assert all(len(r.output) == 6 for r in sched.finished)
+    assert cache.free_pages() == cache.total_pages()
+
+
+def test_requests_that_can_never_run_are_refused_at_submit():
+    sched, cache = make(num_pages=4, page=4, max_seq_len=40)
+    too_long = req("long", 40)
+    assert not sched.submit(too_long) and "max_seq_len" in too_long.finish_reason
+    too_big = req("big", 10, max_tokens=20)                   # 30 tokens = 8 pages > 4
+    assert not sched.submit(too_big) and "pages" in too_big.finish_reason
+    empty = Request("e", [], SamplingParams())
+    assert not sched.submit(empty)
+    clamp = req("clamp", 10, max_tokens=1000)                 # room left: 40 - 10 = 30 -> 10 pages > 4
+    assert not sched.submit(clamp)
+    sched2, _ = make(num_pages=16, page=4, max_seq_len=40)
+    ok = req("ok", 10, max_tokens=1000)
+    assert sched2.submit(ok) and ok.max_tokens == 30          # clamped to the room left
+    assert not sched.has_work()
+
+
+def test_eos_stops_and_wins_over_length_unless_ignored():
+    sched, cache = make(eos=[99])
+    a, b, c = req("a", 2, max_tokens=3), req("b", 2, max_tokens=3, ignore_eos=True), req("c", 2, max_tokens=1)
+    for r in (a, b, c):
+        sched.submit(r)
+    while sched.has_work():
+        run_step(sched, cache, token_of=lambda r: 99)
+    assert (a.output, a.finish_reason) == ([99], "stop")
+    assert (b.output, b.finish_reason) == ([99, 99, 99], "length")
+    assert (c.output, c.finish_reason) == ([99], "stop")      # EOS on the last allowed token: stop
+    d = req("d", 2, max_tokens=5, stop_token_ids=[5])
+    sched.submit(d)
+    while sched.has_work():
+        run_step(sched, cache, token_of=lambda r: 5)
+    assert d.finish_reason == "stop"
+
+
+def test_abort_gives_everything_back():
+    sched, cache = make(budget=4)
+    sched.submit(req("a", 10))
+    sched.submit(req("b", 3))
+    run_step(sched, cache)                                    # a is half-way through its prompt
+    assert sched.abort("a") and sched.abort("b") and not sched.abort("nobody")
+    sched.check_integrity()
+    assert cache.free_pages() == cache.total_pages() and not sched.has_work()
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_workloads_finish_with_nothing_left_behind(seed):
+    rng = random.Random(seed)
+    sched, cache = make(num_pages=rng.randint(8, 20), page=rng.choice([2, 4, 8]),
+                        slots=rng.randint(1, 4), max_seq_len=64, budget=rng.randint(2, 12))
+    accepted = []
+    for i in range(12):
+        r = req(f"r{i}", rng.randint(1, 30), max_tokens=rng.randint(1, 12))
+        if sched.submit(r):
+            accepted.append(r)
+    steps = 0
+    while sched.has_work():
+        plan, _ = run_step(sched, cache, token_of=lambda r: rng.randint(0, 50))
+        assert plan and sum(len(e.tokens) for e in plan if not e.samples or len(e.tokens) > 1) <= sched.max_step_tokens
+        steps += 1
+        assert steps < 2000
+    assert all(r.finish_reason == "length" and len(r.output) == r.max_tokens for r in accepted)
+    assert cache.free_pages() == cache.total_pages() and cache.free_slots == cache.max_slots
