@@ -136,6 +136,22 @@ def prefill_flops(cfg: Dict[str, Any], layers: int, tokens: int) -> float:
     return layers * (per_token * tokens + attn) + 2 * V * H
 
 
+def reference_unavailable() -> str:
+    """Why the reference arm cannot run: tried against ``baseline/_ref``."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "freetoken")):
+        return ("the reference is not installed under baseline/_ref: pip cannot resolve its pinned "
+                "dependencies offline (apache-tvm-ffi==0.1.13.post3, flashlib==0.3.0 are not in the wheelhouse)")
+    probe = subprocess.run([sys.executable, "-c", "import freetoken.llm"], capture_output=True, text=True,
+                           env={**os.environ, "PYTHONPATH": ref})
+    if probe.returncode != 0:
+        last = (probe.stderr.strip().splitlines() or ["import failed"])[-1]
+        return ("installed with --no-deps, but its public API does not import here: " + last +
+                " (flashlib is a hard dependency that is not in the wheelhouse)")
+    return ("its MiniMax-M3 path serves NVFP4 experts through the expert offload cache only; there is "
+            "no bfloat16 resident-weight configuration of this model to time")
+
+
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="bench.py")
     p.add_argument("--gpus", type=int, default=1)
@@ -155,10 +171,7 @@ def build_parser() -> argparse.ArgumentParser:
 def main(argv: Optional[List[str]] = None) -> int:
     a = build_parser().parse_args(argv)
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference does not install offline: its hard dependency "
-                          "flashlib==0.3.0 is not in the wheelhouse and it has no float/bf16 "
-                          "MiniMax-M3 path without its NVFP4 offload cache"}))
+        print(json.dumps({"impl": "reference", "unavailable": reference_unavailable()}))
         return 0
     if a.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {a.gpus} is not supported (use --gpus 1)")

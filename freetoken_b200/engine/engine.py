@@ -85,7 +85,7 @@ class Engine:
             free_before = torch.cuda.mem_get_info(self.device)[0]
         self.plan = arch.build_plan(config)
         self.model = Model(self.plan)
-        build.ensure_built(self.model.libraries(self.dtype) + ["sampling"])
+        build.ensure_built(self.model.libraries(self.dtype))
         specs = self.model.tensor_specs()
         if tensors is None and folder is not None:
             tensors = load_tensors(specs, folder, self.dtype, self.device, arch.rename_tensor,
@@ -366,6 +366,11 @@ class Engine:
         ops.LAUNCHES += graph[1]
         self.graph_replays += 1
         return True
+
+    def check_status(self) -> None:
+        """Raise if a kernel recorded a failure (a bounded wait that ran out)
+        since the last check.  Synchronises the device."""
+        ops.check_tc_status(self.device)
 
     # ---- reporting ---------------------------------------------------------------
     def stats(self) -> Dict[str, Any]:

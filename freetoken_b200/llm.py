@@ -78,6 +78,7 @@ class LLM:
         self.sampler = Sampler(self.engine.device, self.engine.vocab_size)
         self.tokenizer = None
         self._counter = 0
+        self.steps_since_check = 0
 
     # ---- text ------------------------------------------------------------
     def _tokenizer(self):
@@ -111,6 +112,7 @@ class LLM:
             self.scheduler.submit(r)
         while self.scheduler.has_work():
             self.run_step(rngs)
+        self.engine.check_status()
         self.scheduler.finished.clear()
         results = []
         for r in requests:
@@ -135,4 +137,8 @@ class LLM:
             params = [r.params for r in samplers]
             uniforms = [0.0 if r.params.is_greedy else rngs[r.id].next_uniform() for r in samplers]
             sampled = self.sampler.sample(logits, params, uniforms).cpu().tolist()
+            self.steps_since_check += 1
+            if self.steps_since_check >= 64:
+                self.steps_since_check = 0
+                self.engine.check_status()
         return self.scheduler.complete(plan, sampled)

@@ -66,6 +66,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             logits = engine.step(entries)
             if logits.shape[0]:
                 torch.cuda.synchronize()
+                engine.check_status()
                 arr = logits.detach().cpu().numpy().astype("<f4", copy=False)
                 arr.tofile(os.path.join(args.out, f"{step['step']}.f32"))
         for rid in step.get("end", []):
