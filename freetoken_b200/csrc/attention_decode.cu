@@ -49,6 +49,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
   __nv_bfloat16* sV = sK + STAGES * TILE * LD;                            // [STAGES][TILE][LD]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
+  pdl_wait();
+
   const int G = a.nq / a.nkv;
   const int gtiles = (G + 15) / 16;
   const int kvh = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
@@ -246,6 +248,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, const int* __restrict__ rows,
                                   int nq, int d, int splits) {
+  pdl_wait();
+
   const int row = blockIdx.x, head = blockIdx.y;
   const int tok = rows ? rows[row] : row;
   const size_t base = ((size_t)row * nq + head) * splits;
@@ -278,7 +282,7 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(a.n_rows, a.nkv * ((G + 15) / 16), a.splits);
-  attn_decode_kernel<D><<<grid, 128, smem, stream>>>(a);
+  launch_pdl(attn_decode_kernel<D>, grid, dim3(128), smem, stream, a);
   return FT_OK;
 }
 
@@ -309,7 +313,7 @@ extern "C" int ft_attn_decode(const void* q, void* out, float* part_o, float* pa
   if (rc != FT_OK) return rc;
   if (splits > 1) {
     dim3 grid(n_rows, nq);
-    attn_merge_kernel<<<grid, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, rows, nq, d, splits);
+    launch_pdl(attn_merge_kernel, grid, dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, rows, nq, d, splits);
   }
   FT_LAUNCH_CHECK();
   return FT_OK;

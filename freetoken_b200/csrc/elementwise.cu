@@ -22,6 +22,8 @@ namespace ft {
 template <typename WT>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
                                     float* __restrict__ residual, int H, int vocab) {
+  pdl_wait();
+
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;  // validated on the host; never index outside the table
@@ -34,15 +36,77 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __res
 // residual (float32) is updated in place with delta when delta != nullptr.
 // delta holds k rows per token (k > 1: the partial results of a token's k
 // routes); they are added in ascending order in float32, then to the residual.
-template <typename AT>
-__global__ void rmsnorm_kernel(const AT* __restrict__ delta, float* __restrict__ residual,
-                               const float* __restrict__ weight, AT* __restrict__ out, int H,
-                               float eps, int plus_one, int k) {
+// A thread owns groups of 4 consecutive elements (element 4*(tid + j*blockDim));
+// up to NORM_KEEP groups stay in registers between the two passes.
+constexpr int NORM_THREADS = 512;
+constexpr int NORM_KEEP = 4;
+
+__device__ __forceinline__ float4 load4f(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4f(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4f(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename AT, bool VEC>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_kernel(const AT* __restrict__ delta, float* __restrict__ residual,
+               const float* __restrict__ weight, AT* __restrict__ out, int H, float eps,
+               int plus_one, int k) {
   __shared__ float scratch[33];
+  pdl_wait();
   const int t = blockIdx.x;
   float* r = residual + (size_t)t * H;
   const AT* d = delta ? delta + (size_t)t * k * H : nullptr;
+  AT* o = out + (size_t)t * H;
+  const float one = plus_one ? 1.f : 0.f;
   float ss = 0.f;
+  if (VEC) {
+    float4 keep[NORM_KEEP];
+    const int groups = H >> 2;
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; ++j) {
+      const int gi = threadIdx.x + j * NORM_THREADS;
+      if (gi < groups) {
+        float4 z = load4f(r + 4 * gi);
+        if (d) {
+          float4 add = load4f(d + 4 * gi);
+          for (int q = 1; q < k; ++q) {
+            const float4 more = load4f(d + (size_t)q * H + 4 * gi);
+            add.x += more.x; add.y += more.y; add.z += more.z; add.w += more.w;
+          }
+          z.x += add.x; z.y += add.y; z.z += add.z; z.w += add.w;
+          store4f(r + 4 * gi, z);
+        }
+        keep[j] = z;
+        ss += z.x * z.x;
+        ss += z.y * z.y;
+        ss += z.z * z.z;
+        ss += z.w * z.w;
+      }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; ++j) {
+      const int gi = threadIdx.x + j * NORM_THREADS;
+      if (gi < groups) {
+        const float4 w = load4f(weight + 4 * gi);
+        const float4 z = keep[j];
+        store4f(o + 4 * gi, make_float4(z.x * inv * (w.x + one), z.y * inv * (w.y + one),
+                                        z.z * inv * (w.z + one), z.w * inv * (w.w + one)));
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float z = r[i];
     if (d) {
@@ -55,8 +119,6 @@ __global__ void rmsnorm_kernel(const AT* __restrict__ delta, float* __restrict__
   }
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)H + eps);
-  AT* o = out + (size_t)t * H;
-  const float one = plus_one ? 1.f : 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     o[i] = from_float<AT>(r[i] * inv * (weight[i] + one));
   }
@@ -84,6 +146,8 @@ struct QkRopeArgs {
 
 template <typename AT>
 __global__ void qk_rope_store_kernel(QkRopeArgs a) {
+  pdl_wait();
+
   extern __shared__ float head_inv[];  // [nq + nkv] for per-head mode
   __shared__ float scratch[33];
   const int t = blockIdx.x;
@@ -211,6 +275,8 @@ __device__ __forceinline__ float sumsq8(const Chunk8& c) {
 }
 
 __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
+  pdl_wait();
+
   extern __shared__ float head_inv[];
   __shared__ float scratch[33];
   const int t = blockIdx.x;
@@ -306,6 +372,8 @@ __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
 // out[t,:] = sum_j parts[t*k+j,:] in float32, j ascending.
 template <typename AT>
 __global__ void combine_kernel(const AT* __restrict__ parts, AT* __restrict__ out, int k, int H) {
+  pdl_wait();
+
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float s = 0.f;
@@ -318,6 +386,8 @@ __global__ void combine_kernel(const AT* __restrict__ parts, AT* __restrict__ ou
 template <typename AT>
 __global__ void gather_rows_kernel(const AT* __restrict__ src, const int* __restrict__ rows,
                                    AT* __restrict__ dst, int H) {
+  pdl_wait();
+
   const int r = blockIdx.x;
   const AT* s = src + (size_t)rows[r] * H;
   AT* d = dst + (size_t)r * H;
@@ -334,7 +404,7 @@ int ft_embed_gather(const int* ids, const void* table, int table_dtype, float* r
                     int H, int vocab, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   FT_DISPATCH(table_dtype, WT,
-              embed_gather_kernel<WT><<<T, 256, 0, stream>>>(ids, (const WT*)table, residual, H, vocab));
+              launch_pdl(embed_gather_kernel<WT>, dim3(T), dim3(256), 0, stream, ids, (const WT*)table, residual, H, vocab));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -343,9 +413,18 @@ int ft_rmsnorm(const void* delta, float* residual, const float* weight, void* ou
                int T, int H, float eps, int plus_one, int k, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if (k < 1) return FT_ERR_SHAPE;
-  FT_DISPATCH(dtype, AT,
-              rmsnorm_kernel<AT><<<T, 256, 0, stream>>>((const AT*)delta, residual, weight,
-                                                        (AT*)out, H, eps, plus_one, k));
+  // 16-byte pieces when the row allows it and fits the registers kept between the passes
+  const bool vec = !(H & 3) && H <= 4 * NORM_THREADS * NORM_KEEP && !((uintptr_t)delta & 15) &&
+                   !((uintptr_t)residual & 15) && !((uintptr_t)weight & 15) && !((uintptr_t)out & 15);
+  if (vec) {
+    FT_DISPATCH(dtype, AT,
+                launch_pdl(rmsnorm_kernel<AT, true>, dim3(T), dim3(NORM_THREADS), 0, stream,
+                           (const AT*)delta, residual, weight, (AT*)out, H, eps, plus_one, k));
+  } else {
+    FT_DISPATCH(dtype, AT,
+                launch_pdl(rmsnorm_kernel<AT, false>, dim3(T), dim3(NORM_THREADS), 0, stream,
+                           (const AT*)delta, residual, weight, (AT*)out, H, eps, plus_one, k));
+  }
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -366,18 +445,18 @@ int ft_qk_rope_store(const void* qkv, void* q_out, void* kv_pages, const float* 
                        !((uintptr_t)kv_pages & 15) && !(ld & 7) && !(page_stride & 7) &&
                        !(kv_stride & 7);
   if (dtype == FT_DTYPE_BF16 && aligned && !(d & 7) && !(R & 15) && !interleaved) {
-    qk_rope_store_vec_kernel<<<T, 256, smem, stream>>>(a);
+    launch_pdl(qk_rope_store_vec_kernel, dim3(T), dim3(256), smem, stream, a);
     FT_LAUNCH_CHECK();
     return FT_OK;
   }
-  FT_DISPATCH(dtype, AT, qk_rope_store_kernel<AT><<<T, 256, smem, stream>>>(a));
+  FT_DISPATCH(dtype, AT, launch_pdl(qk_rope_store_kernel<AT>, dim3(T), dim3(256), smem, stream, a));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
 
 int ft_combine(const void* parts, void* out, int dtype, int T, int k, int H, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
-  FT_DISPATCH(dtype, AT, combine_kernel<AT><<<T, 256, 0, stream>>>((const AT*)parts, (AT*)out, k, H));
+  FT_DISPATCH(dtype, AT, launch_pdl(combine_kernel<AT>, dim3(T), dim3(256), 0, stream, (const AT*)parts, (AT*)out, k, H));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -386,7 +465,7 @@ int ft_gather_rows(const void* src, const int* rows, void* dst, int dtype, int n
                    cudaStream_t stream) {
   if (n <= 0) return FT_OK;
   FT_DISPATCH(dtype, AT,
-              gather_rows_kernel<AT><<<n, 256, 0, stream>>>((const AT*)src, rows, (AT*)dst, H));
+              launch_pdl(gather_rows_kernel<AT>, dim3(n), dim3(256), 0, stream, (const AT*)src, rows, (AT*)dst, H));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

@@ -19,6 +19,8 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
                                      int k, int softmax_scoring, int renormalize, float scale) {
   extern __shared__ float smem[];  // [WARPS][2][E]: scores, choice values
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_wait();
+
   const int t = blockIdx.x * WARPS + warp;
   if (t >= T) return;
   float* score = smem + (size_t)warp * 2 * E;
@@ -42,6 +44,8 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   for (int e = lane; e < E; e += 32) choice[e] = score[e] + (bias ? bias[e] : 0.f);
   __syncwarp();
   float wsum = 0.f;
+  int my_id = 0;        // lane j keeps the j-th choice (k <= 32), else it goes through memory
+  float my_w = 0.f;
   for (int j = 0; j < k; ++j) {
     float best = -INFINITY;
     int arg = 0x7fffffff;
@@ -58,14 +62,21 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     if (arg == 0x7fffffff) arg = 0;  // all values NaN or -inf: stay in range
     const float w = score[arg];
     wsum += w;
-    if (lane == 0) {
-      ids[(size_t)t * k + j] = arg;
-      weights[(size_t)t * k + j] = w;
-      choice[arg] = -INFINITY;
+    if (lane == (j & 31)) {
+      if (k <= 32) { my_id = arg; my_w = w; }
+      else { ids[(size_t)t * k + j] = arg; weights[(size_t)t * k + j] = w; }
     }
+    if (lane == 0) choice[arg] = -INFINITY;
     __syncwarp();
   }
-  if (lane == 0) {
+  if (k <= 32) {
+    if (lane < k) {
+      float w = my_w;
+      if (renormalize) w = w / (wsum + 1e-20f);
+      ids[(size_t)t * k + lane] = my_id;
+      weights[(size_t)t * k + lane] = w * scale;
+    }
+  } else if (lane == 0) {
     for (int j = 0; j < k; ++j) {
       float w = weights[(size_t)t * k + j];
       if (renormalize) w = w / (wsum + 1e-20f);
@@ -97,35 +108,49 @@ __device__ __forceinline__ void load8f(const __nv_bfloat16* p, float (&v)[8]) {
 }
 
 template <typename AT>
-__global__ void router_logits_kernel(const AT* __restrict__ x, long long ldx,
-                                     const float* __restrict__ W, float* __restrict__ logits,
-                                     int T, int E, int H) {
+__global__ void __launch_bounds__(128) router_logits_kernel(const AT* __restrict__ x, long long ldx,
+                                                            const float* __restrict__ W,
+                                                            float* __restrict__ logits, int T, int E,
+                                                            int H) {
+  // one block per (expert, 8 tokens); its 4 warps take a quarter of the row
+  // each (pieces p = warp, warp+4, ... of 256 values) and their partial sums are
+  // added in warp order
   constexpr int TT = 8;
-  const int lane = threadIdx.x & 31;
-  const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  __shared__ float part[4][TT];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = blockIdx.x;
   const int t0 = blockIdx.y * TT;
-  if (e >= E) return;
+  pdl_wait();
   const float* w = W + (size_t)e * H;
   float acc[TT];
 #pragma unroll
   for (int i = 0; i < TT; ++i) acc[i] = 0.f;
-  for (int h = lane * 8; h < H; h += 256) {
+#pragma unroll 2
+  for (int h = warp * 256 + lane * 8; h < H; h += 1024) {
     float wv[8];
     load8f(w + h, wv);
+    float xv[TT][8];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+      if (t0 + tt < T) load8f(x + (size_t)(t0 + tt) * ldx + h, xv[tt]);
+    }
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
       if (t0 + tt < T) {
-        float xv[8];
-        load8f(x + (size_t)(t0 + tt) * ldx + h, xv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[tt] = fmaf(xv[i], wv[i], acc[tt]);
+        for (int i = 0; i < 8; ++i) acc[tt] = fmaf(xv[tt][i], wv[i], acc[tt]);
       }
     }
   }
 #pragma unroll
   for (int tt = 0; tt < TT; ++tt) {
     const float v = warp_sum(acc[tt]);
-    if (lane == 0 && t0 + tt < T) logits[(size_t)(t0 + tt) * E + e] = v;
+    if (lane == 0) part[warp][tt] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < TT && t0 + threadIdx.x < T) {
+    const int tt = threadIdx.x;
+    logits[(size_t)(t0 + tt) * E + e] = ((part[0][tt] + part[1][tt]) + part[2][tt]) + part[3][tt];
   }
 }
 
@@ -134,6 +159,8 @@ constexpr int SCAN = 8;  // route ids a lane reads ahead while scanning
 // counts[e] = number of routes that chose expert e.  One warp per expert.
 __global__ void moe_count_kernel(const int* __restrict__ ids, int* __restrict__ counts, int R, int E) {
   const int lane = threadIdx.x & 31;
+  pdl_wait();
+
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (e >= E) return;
   int c = 0;
@@ -158,6 +185,8 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
                                    int* __restrict__ sorted_token, int* __restrict__ active,
                                    int R, int E, int k) {
   const int lane = threadIdx.x & 31;
+  pdl_wait();
+
   const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (e >= E) return;
   int before = 0, busy_before = 0;
@@ -220,8 +249,8 @@ int ft_router_select(const float* logits, const float* bias, int* ids, float* we
   if (smem > 200 * 1024) return FT_ERR_SHAPE;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(router_select_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  router_select_kernel<WARPS><<<(T + WARPS - 1) / WARPS, WARPS * 32, smem, stream>>>(
-      logits, bias, ids, weights, T, E, k, softmax_scoring, renormalize, scale);
+  launch_pdl(router_select_kernel<WARPS>, dim3((T + WARPS - 1) / WARPS), dim3(WARPS * 32), smem, stream,
+             logits, bias, ids, weights, T, E, k, softmax_scoring, renormalize, scale);
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -230,10 +259,9 @@ int ft_router_logits(const void* x, int x_dtype, long long ldx, const float* W, 
                      int T, int E, int H, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if ((H & 7) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return FT_ERR_SHAPE;
-  const int warps = 4;
-  dim3 grid((E + warps - 1) / warps, (T + 7) / 8);
+  dim3 grid(E, (T + 7) / 8);
   FT_DISPATCH(x_dtype, AT,
-              router_logits_kernel<AT><<<grid, warps * 32, 0, stream>>>((const AT*)x, ldx, W, logits, T, E, H));
+              launch_pdl(router_logits_kernel<AT>, grid, dim3(128), 0, stream, (const AT*)x, ldx, W, logits, T, E, H));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -243,9 +271,9 @@ int ft_moe_sort(const int* ids, int* counts, int* offsets, int* sorted_route, in
   if (R <= 0) return FT_OK;
   const int warps = 4;
   const int blocks = (E + warps - 1) / warps;
-  moe_count_kernel<<<blocks, warps * 32, 0, stream>>>(ids, counts, R, E);
-  moe_scatter_kernel<<<blocks, warps * 32, 0, stream>>>(ids, counts, offsets, sorted_route,
-                                                        sorted_token, active, R, E, k);
+  launch_pdl(moe_count_kernel, dim3(blocks), dim3(warps * 32), 0, stream, ids, counts, R, E);
+  launch_pdl(moe_scatter_kernel, dim3(blocks), dim3(warps * 32), 0, stream, ids, (const int*)counts, offsets,
+             sorted_route, sorted_token, active, R, E, k);
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

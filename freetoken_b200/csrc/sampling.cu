@@ -52,6 +52,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   __shared__ float scratch[33];
   __shared__ float prefix[SAMPLE_THREADS];
   __shared__ int winner;
+  pdl_wait();
+
   const int row = blockIdx.x;
   const float* x = logits + (size_t)row * V;
   const float T = temperature ? temperature[row] : 0.f;

@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(KS * 32) skinny_kernel(SkinnyArgs a) {
   constexpr int NG = GLU ? 2 : 1;
   __shared__ float red[KS][NT][NG][16][8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  pdl_wait();
+
   int group = blockIdx.y;
   if (a.active) {
     if ((int)blockIdx.y >= a.active[a.G]) return;
@@ -185,9 +187,9 @@ __global__ void __launch_bounds__(KS * 32) skinny_kernel(SkinnyArgs a) {
 template <bool GLU, typename OT>
 int launch_nt(const SkinnyArgs& a, int nt, dim3 grid, cudaStream_t stream) {
   switch (nt) {
-    case 1: skinny_kernel<1, GLU, OT><<<grid, KS * 32, 0, stream>>>(a); break;
-    case 2: skinny_kernel<2, GLU, OT><<<grid, KS * 32, 0, stream>>>(a); break;
-    case 4: skinny_kernel<4, GLU, OT><<<grid, KS * 32, 0, stream>>>(a); break;
+    case 1: launch_pdl(skinny_kernel<1, GLU, OT>, grid, dim3(KS * 32), 0, stream, a); break;
+    case 2: launch_pdl(skinny_kernel<2, GLU, OT>, grid, dim3(KS * 32), 0, stream, a); break;
+    case 4: launch_pdl(skinny_kernel<4, GLU, OT>, grid, dim3(KS * 32), 0, stream, a); break;
     default: return FT_ERR_SHAPE;
   }
   return FT_OK;
