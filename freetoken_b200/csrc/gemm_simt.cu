@@ -151,8 +151,95 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(GemmArgs a) {
   }
 }
 
+// Dense product for many rows: the same arithmetic (every output element is
+// one thread's fma chain over ascending k, so results are bit-identical to
+// gemm_rows_kernel) with 16-byte global loads, k-major shared tiles and
+// 128-bit shared loads.  Needs K % 32 == 0 and 16-byte aligned rows.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <typename AT, typename WT, typename OT>
+__global__ void __launch_bounds__(256) gemm_dense_kernel(GemmArgs a) {
+  constexpr int TBM = 64, TBN = 64, TBK = 32;
+  __shared__ __align__(16) float As[TBK][TBM + 4];
+  __shared__ __align__(16) float Ws[TBK][TBN + 4];
+  const int row0 = blockIdx.x * TBM, n0 = blockIdx.y * TBN;
+  const AT* A = (const AT*)a.A;
+  const WT* W = (const WT*)a.W;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 8;      // this thread loads row lr, k lk..lk+7
+  const bool a_ok = row0 + lr < a.M, w_ok = n0 + lr < a.N;
+  const AT* ap = A + (size_t)(a_ok ? row0 + lr : 0) * a.lda + lk;
+  const WT* wp = W + (size_t)(w_ok ? n0 + lr : 0) * a.K + lk;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  float av[8], wv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) av[i] = wv[i] = 0.f;
+  if (a_ok) load8(ap, av);
+  if (w_ok) load8(wp, wv);
+  for (int k0 = 0; k0 < a.K; k0 += TBK) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      As[lk + i][lr] = av[i];
+      Ws[lk + i][lr] = wv[i];
+    }
+    __syncthreads();
+    if (k0 + TBK < a.K) {            // next tile's loads fly while this one is multiplied
+      if (a_ok) load8(ap + k0 + TBK, av);
+      if (w_ok) load8(wp + k0 + TBK, wv);
+    }
+#pragma unroll
+    for (int kk = 0; kk < TBK; ++kk) {
+      const float4 a4 = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      const float4 w4 = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
+      const float ar[4] = {a4.x, a4.y, a4.z, a4.w}, wr[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  OT* C = (OT*)a.C;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = row0 + ty * 4 + i;
+    if (r >= a.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < a.N) C[(size_t)r * a.ldc + n] = from_float<OT>(acc[i][j]);
+    }
+  }
+}
+
 template <typename AT, typename WT, typename OT>
 int launch(const GemmArgs& a, int glu, int max_tiles_hint, cudaStream_t stream) {
+  const bool plain = !glu && !a.group_offsets && !a.a_rows && !a.c_rows && !a.row_scale;
+  const int a_align = sizeof(AT) == 2 ? 7 : 3, w_align = sizeof(WT) == 2 ? 7 : 3;
+  if (plain && a.M >= 64 && !(a.K & 31) && !(a.lda & a_align) && !(a.K & w_align) &&
+      !((uintptr_t)a.A & 15) && !((uintptr_t)a.W & 15)) {
+    dim3 grid((a.M + 63) / 64, (a.N + 63) / 64);
+    gemm_dense_kernel<AT, WT, OT><<<grid, 256, 0, stream>>>(a);
+    return FT_OK;
+  }
   const int per_group = a.group_offsets ? a.M / max(a.G, 1) : a.M;
   const bool big = per_group >= 32;
   const int bm = big ? 64 : 16;

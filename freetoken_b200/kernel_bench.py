@@ -1,0 +1,190 @@
+"""One kernel on one small, real-width workload: time it, print its roofline share.
+
+    python -m freetoken_b200.kernel_bench --kernel expert_gemv [--reps 20]
+
+Used by hand and as the program profiled under ``ncu`` (the summaries under
+``profiles/`` name the command).  Workloads hold well under 2 GB on the device
+and are larger than the L2 cache; the input that is streamed is rotated between
+repetitions so that no repetition finds it in L2.
+
+Kernels: ``expert_gemv`` (decode experts, weight-streaming mma.sync kernel),
+``lm_head`` (the same kernel, dense, float32 result), ``moe_gemm_tc`` (prefill
+experts on tcgen05/TMEM with TMA), ``attn_decode``, ``attn_prefill``,
+``router`` (float32 router logits + top-k for a decode batch).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from typing import Callable, Dict, Tuple
+
+import torch
+
+from .benchmark import load_peaks
+from .csrc import ops
+from .parts.base import Workspace
+
+H, I, D, NQ, NKV = 3072, 1536, 128, 48, 8
+DEV = "cuda:0"
+
+
+def _routes(experts: int, tokens: int, k: int, seed: int = 0):
+    """Sorted routes of ``tokens`` tokens choosing ``k`` of ``experts`` uniformly."""
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(tokens)]).to(torch.int32)
+    flat = ids.view(-1)
+    order = torch.sort(flat.long(), stable=True).indices.to(torch.int32)
+    counts = torch.bincount(flat.long(), minlength=experts)
+    offsets = torch.zeros(experts + 1, dtype=torch.int32)
+    offsets[1:] = counts.cumsum(0)
+    busy = (counts > 0).nonzero().flatten().to(torch.int32)
+    active = torch.zeros(experts + 1, dtype=torch.int32)
+    active[:busy.numel()] = busy
+    active[experts] = busy.numel()
+    dev = lambda t: t.to(DEV)
+    return dev(order), dev((order // k).to(torch.int32)), dev(offsets), dev(active), int(busy.numel())
+
+
+def expert_gemv(sets: int = 2):
+    """Decode, batch 8: 64 routes over 48 experts, gate_up + GLU then down."""
+    E, T, k = 48, 8, 8
+    w1 = [torch.randn(E, 2 * I, H, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
+    w2 = [torch.randn(E, H, I, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    route, token, offsets, active, busy = _routes(E, T, k)
+    R = T * k
+    mid = torch.empty(R, I, device=DEV, dtype=torch.bfloat16)
+    parts = torch.empty(R, H, device=DEV, dtype=torch.bfloat16)
+    rw = torch.rand(R, device=DEV)
+
+    def run(i):
+        ops.skinny_gemm(x, w1[i % sets], mid, group_offsets=offsets, active=active, a_rows=token, rows=R, glu=True)
+        ops.skinny_gemm(mid, w2[i % sets], parts, group_offsets=offsets, active=active, c_rows=route,
+                        row_scale=rw, rows=R)
+    return run, busy * 3 * I * H * 2, 0.0, "hbm"
+
+
+def lm_head(sets: int = 2):
+    V, T = 200064, 8
+    w = [torch.randn(V, H, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(T, V, device=DEV)
+    return (lambda i: ops.skinny_gemm(x, w[i % sets], out)), V * H * 2, 0.0, "hbm"
+
+
+def moe_gemm_tc(sets: int = 2):
+    """Prefill: 256 tokens x 8 routes over 32 experts (64 rows each)."""
+    E, T, k = 32, 256, 8
+    w1 = [torch.randn(E, 2 * I, H, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
+    w2 = [torch.randn(E, H, I, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    route, token, offsets, active, busy = _routes(E, T, k)
+    R = T * k
+    ws = Workspace(DEV)
+    xs = torch.empty(R, H, device=DEV, dtype=torch.bfloat16)
+    ops.gather_rows(x, token, xs)
+    mid = torch.empty(R, I, device=DEV, dtype=torch.bfloat16)
+    parts = torch.empty(R, H, device=DEV, dtype=torch.bfloat16)
+    rw = torch.rand(R, device=DEV)
+    ntok = ops.tc_tokens_per_tile(R, E)
+    tiles = ops.moe_tile_map(offsets, active, R, E, ntok, ws)
+
+    def run(i):
+        ops.moe_gemm_tc(xs, w1[i % sets], mid, group_offsets=offsets, active=active, tile_map=tiles, rows=R,
+                        glu=True, tokens_per_tile=ntok)
+        ops.moe_gemm_tc(mid, w2[i % sets], parts, group_offsets=offsets, active=active, tile_map=tiles,
+                        c_rows=route, row_scale=rw, rows=R, tokens_per_tile=ntok)
+    return run, busy * 3 * I * H * 2, 2.0 * R * 3 * I * H, "hbm"
+
+
+def _kv(batch: int, ctx: int, sets: int):
+    P = 64
+    width = ctx // P
+    pages = batch * width + 1
+    kv = [torch.randn(2, pages, NKV, P, D, device=DEV, dtype=torch.bfloat16) for _ in range(sets)]
+    table = (torch.randperm(pages - 1)[: batch * width] + 1).to(torch.int32).view(batch, width).to(DEV)
+    return kv, table
+
+
+def attn_decode(sets: int = 2):
+    B, ctx = 64, 2048
+    kv, table = _kv(B, ctx, sets)
+    q = torch.randn(B, NQ * D, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
+    seg = torch.arange(B, dtype=torch.int32, device=DEV)
+    ws = Workspace(DEV)
+
+    def run(i):
+        ops.attn_decode(q, out, kv[i % sets], None, B, pos, seg, table, NQ, NKV, D, D ** -0.5, None, ctx, ws)
+    return run, B * ctx * 2 * NKV * D * 2, 4.0 * B * NQ * D * ctx, "hbm"
+
+
+def attn_prefill(sets: int = 1):
+    T = 2048
+    kv, table = _kv(1, T, sets)
+    q = torch.randn(T, NQ * D, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
+    tiles = list(range(0, T, 64))
+
+    def run(i):
+        ops.attn_prefill(q, out, kv[0], i32([0] * len(tiles)), i32(tiles), i32([0, T]), i32([0]), table,
+                         NQ, NKV, D, D ** -0.5, None)
+    return run, 0, 4.0 * NQ * D * (T * (T + 1) / 2), "tensor"
+
+
+def router(sets: int = 8):
+    E, T, k = 256, 8, 8
+    w = [torch.randn(E, H, device=DEV) * 0.02 for _ in range(sets)]
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    logits = torch.empty(T, E, device=DEV)
+    ids = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    wts = torch.empty(T, k, device=DEV)
+
+    def run(i):
+        ops.router_logits(x, w[i % sets], logits)
+        ops.router_select(logits, None, ids, wts, k, False, True, 1.0)
+    return run, E * H * 4, 0.0, "hbm"
+
+
+KERNELS: Dict[str, Callable[[], Tuple[Callable[[int], None], int, float, str]]] = {
+    "expert_gemv": expert_gemv, "lm_head": lm_head, "moe_gemm_tc": moe_gemm_tc,
+    "attn_decode": attn_decode, "attn_prefill": attn_prefill, "router": router,
+}
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(prog="kernel_bench")
+    p.add_argument("--kernel", required=True, choices=sorted(KERNELS))
+    p.add_argument("--reps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=3)
+    a = p.parse_args(argv)
+    run, nbytes, flops, bound = KERNELS[a.kernel]()
+    for i in range(a.warmup):
+        run(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(a.reps):
+        run(a.warmup + i)
+    end.record()
+    torch.cuda.synchronize()
+    ops.check_tc_status(DEV)
+    ms = start.elapsed_time(end) / a.reps
+    peaks = load_peaks()
+    out = {"kernel": a.kernel, "ms": ms, "bytes": nbytes, "flops": flops, "peaks": peaks["source"]}
+    if nbytes:
+        out["GB/s"] = nbytes / ms / 1e6
+        out["hbm_frac"] = out["GB/s"] / peaks["hbm_gbs"]
+    if flops:
+        out["TFLOP/s"] = flops / ms / 1e9
+        out["tensor_frac"] = out["TFLOP/s"] / peaks["bf16_tflops"]
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

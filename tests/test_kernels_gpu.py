@@ -158,7 +158,7 @@ GEMM_TYPES = [("float32", "float32", "float32"), ("float32", "bfloat16", "float3
 
 
 @pytest.mark.parametrize("at,wt,ct", GEMM_TYPES)
-@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (9, 100, 96), (70, 130, 257)])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (9, 100, 96), (70, 130, 257), (200, 130, 96)])
 def test_gemm_rows_dense(at, wt, ct, M, N, K):
     a = rnd(M, K, dtype=DT[at], seed=1)
     w = rnd(N, K, dtype=DT[wt], seed=2, scale=0.1)
@@ -167,6 +167,11 @@ def test_gemm_rows_dense(at, wt, ct, M, N, K):
     want = a.float() @ w.float().t()
     tol = TOL["bfloat16" if ct == "bfloat16" else "float32"]
     assert torch.allclose(c.float(), want, atol=tol["atol"] * 3, rtol=tol["rtol"])
+    if M >= 64 and K % 32 == 0:
+        # many rows take the tiled kernel, few rows the simple one: the same bits
+        few = torch.empty(8, N, dtype=DT[ct], device=DEV)
+        ops().gemm_rows(a[100:108], w, few)
+        assert torch.equal(few, c[100:108])
 
 
 def _grouped_case(E, k, T, seed=0):
