@@ -52,12 +52,15 @@ class LMHead(Head):
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
         self.tied_to = spec.get("tied_to")
-        self.weight_name = self.tied_to or self.name(f"{spec.params['scope']}.weight")
+        self.own_name = self.name(f"{spec.params['scope']}.weight")
+        self.weight_name = self.tied_to or self.own_name
         self.weight = None
 
     def tensor_specs(self) -> List[TensorSpec]:
         if self.tied_to:
-            return []
+            # a checkpoint of a tied model may still carry the head's tensor; it
+            # is accepted and dropped (python/freetoken/layers/embedding.py:74-90)
+            return [TensorSpec(self.own_name, (self.vocab, self.hidden), optional=True, keep=False)]
         return [TensorSpec(self.weight_name, (self.vocab, self.hidden))]
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype) -> None:

@@ -138,7 +138,7 @@ def load_tensors(
         out: Dict[str, torch.Tensor] = {}
         for i, spec in enumerate(specs):
             src = chosen.get(spec.name)
-            if src is None:
+            if src is None or not spec.keep:
                 continue
             stored = ckpt.entries[alias[leaves(src)[0].name]].dtype
             dtype = device_dtype(spec.role, stored, compute_dtype)
@@ -154,6 +154,7 @@ def check_state(specs: Sequence[TensorSpec], state: Dict[str, torch.Tensor]) -> 
     """Validate an in-memory ``{model-side name: tensor}`` state against specs."""
     missing = [s.name for s in specs if s.name not in state and not s.optional]
     names = {s.name for s in specs}
+    specs = [s for s in specs if s.keep]
     unexpected = sorted(n for n in state if n not in names)
     wrong = [
         (s.name, tuple(s.shape), tuple(state[s.name].shape))

@@ -119,6 +119,9 @@ class TensorSpec:
     # is written in 16 bits (router tensors stay float32 there).
     keep_float32_in_file: bool = False
     optional: bool = False
+    # False: the tensor may be present in a checkpoint (it is checked like any
+    # other) but is not loaded
+    keep: bool = True
     # Which knob of the random-weights mode scales this tensor:
     # "matrix", "norm" or "router_bias".
     tag: str = "matrix"

@@ -67,6 +67,13 @@ def test_float32_files_stay_float32_only_in_float32_mode(tmp_path):
     assert f32[name].dtype == torch.float32 and b16[name].dtype == torch.bfloat16
     assert torch.equal(b16[name], f32[name].to(torch.bfloat16))
     assert "lm_head.weight" not in f32                                   # tied head has no tensor
+    # a tied checkpoint that still carries lm_head.weight is accepted, the tensor dropped
+    raw = read_safetensors(os.path.join(folder, "model.safetensors"))
+    raw["lm_head.weight"] = raw["model.embed_tokens.weight"].clone()
+    os.makedirs(tmp_path / "with_head")
+    write_safetensors(str(tmp_path / "with_head" / "model.safetensors"), raw)
+    again = load_tensors(specs, str(tmp_path / "with_head"), torch.float32, "cpu", arch.rename_tensor)
+    assert torch.equal(again["model.embed_tokens.weight"], f32["model.embed_tokens.weight"])
     assert device_dtype("int32", torch.int64, torch.bfloat16) == torch.int32
 
 
