@@ -155,15 +155,15 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
       const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-      const float al0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - mn0);
-      const float al1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - mn1);
+      const float al0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - mn0);
+      const float al1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - mn1);
       const float base0 = (mn0 == -INFINITY) ? 0.f : mn0, base1 = (mn1 == -INFINITY) ? 0.f : mn1;
       float sum0 = 0.f, sum1 = 0.f;
       unsigned pf[4];
 #pragma unroll
       for (int n = 0; n < 2; ++n) {
-        const float p0 = exp2f(s[n][0] - base0), p1 = exp2f(s[n][1] - base0);
-        const float p2 = exp2f(s[n][2] - base1), p3 = exp2f(s[n][3] - base1);
+        const float p0 = fast_exp2(s[n][0] - base0), p1 = fast_exp2(s[n][1] - base0);
+        const float p2 = fast_exp2(s[n][2] - base1), p3 = fast_exp2(s[n][3] - base1);
         sum0 += p0 + p1;
         sum1 += p2 + p3;
         pf[2 * n] = pack_bf16(p0, p1);
@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = red_ml[(w * 16 + r) * 2];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
       l += red_ml[(w * 16 + r) * 2 + 1] * f;
       acc += red_o[(w * 16 + r) * D + c] * f;
     }
@@ -258,13 +258,13 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   float l = 0.f;
   for (int s = 0; s < splits; ++s) {
     const float ms = part_ml[(base + s) * 2];
-    l += (ms == -INFINITY) ? 0.f : part_ml[(base + s) * 2 + 1] * exp2f(ms - m);
+    l += (ms == -INFINITY) ? 0.f : part_ml[(base + s) * 2 + 1] * fast_exp2(ms - m);
   }
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < splits; ++s) {
       const float ms = part_ml[(base + s) * 2];
-      if (ms != -INFINITY) acc += part_o[(base + s) * d + c] * exp2f(ms - m);
+      if (ms != -INFINITY) acc += part_o[(base + s) * d + c] * fast_exp2(ms - m);
     }
     out[((size_t)tok * nq + head) * d + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
   }

@@ -37,16 +37,21 @@ constexpr int KT = 64;      // keys per tile
 constexpr int PSTAGES = 2;
 
 template <int D>
-__global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
+__global__ void __launch_bounds__(128, 3) attn_prefill_kernel(PrefillArgs a) {
   constexpr int LD = D + 8;
   constexpr int CH = D / 8;
+  static_assert(QT == KT, "the query tile borrows the second K stage");
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [QT][LD]
-  __nv_bfloat16* sK = sQ + QT * LD;                                  // [PSTAGES][KT][LD]
-  __nv_bfloat16* sV = sK + PSTAGES * KT * LD;
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [PSTAGES][KT][LD]
+  __nv_bfloat16* sV = sK + PSTAGES * KT * LD;                        // [PSTAGES][KT][LD]
+  // The query tile is only needed until its fragments sit in registers; it
+  // borrows the second K stage, which the pipeline first fills after that.
+  __nv_bfloat16* sQ = sK + KT * LD;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
-  const int seg = a.tile_seg[blockIdx.x], q0 = a.tile_q0[blockIdx.x];
+  // the list is walked backwards: the tiles with the most keys start first
+  const int tile_index = gridDim.x - 1 - blockIdx.x;
+  const int seg = a.tile_seg[tile_index], q0 = a.tile_q0[tile_index];
   const int head = blockIdx.y;
   const int kvh = head / (a.nq / a.nkv);
   const int seg_begin = a.seg_q_start[seg];
@@ -92,6 +97,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
     const int r = warp * 16 + (lane & 15), c = ks * 16 + (lane >> 4) * 8;
     ldsm_x4(qf[ks], sQ + r * LD + c);
   }
+  __syncthreads();      // every warp has its query fragments: the borrowed stage is free
   float o[D / 8][4];
 #pragma unroll
   for (int nn = 0; nn < D / 8; ++nn)
@@ -146,15 +152,15 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
       const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-      const float al0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - mn0);
-      const float al1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - mn1);
+      const float al0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - mn0);
+      const float al1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - mn1);
       const float base0 = (mn0 == -INFINITY) ? 0.f : mn0, base1 = (mn1 == -INFINITY) ? 0.f : mn1;
       float sum0 = 0.f, sum1 = 0.f;
       unsigned pf[KT / 8][2];
 #pragma unroll
       for (int nt = 0; nt < KT / 8; ++nt) {
-        const float p0 = exp2f(s[nt][0] - base0), p1 = exp2f(s[nt][1] - base0);
-        const float p2 = exp2f(s[nt][2] - base1), p3 = exp2f(s[nt][3] - base1);
+        const float p0 = fast_exp2(s[nt][0] - base0), p1 = fast_exp2(s[nt][1] - base0);
+        const float p2 = fast_exp2(s[nt][2] - base1), p3 = fast_exp2(s[nt][3] - base1);
         sum0 += p0 + p1;
         sum1 += p2 + p3;
         pf[nt][0] = pack_bf16(p0, p1);
@@ -205,7 +211,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
 
 template <int D>
 int launch_prefill(const PrefillArgs& a, int tiles, cudaStream_t stream) {
-  const size_t smem = (size_t)(QT + 2 * PSTAGES * KT) * (D + 8) * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(2 * PSTAGES * KT) * (D + 8) * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>,

@@ -156,8 +156,13 @@ template <bool GLU>
 __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                           const __grid_constant__ CUtensorMap tm_x,
                                                           TcArgs a) {
-  constexpr int STAGES = GLU ? 4 : 6;
-  constexpr int STAGE_BYTES = (GLU ? 2 : 1) * TC_A_BYTES + TC_B_BYTES;
+  // a stage holds KSUB 64-wide k-blocks: one with GLU (two weight boxes per
+  // k-block already), two without, so that every stage moves 40-48 KB and the
+  // per-stage barrier round trip is paid half as often on the down projection
+  constexpr int KSUB = GLU ? 1 : 2;
+  constexpr int NA = GLU ? 2 : 1;                     // weight boxes per k-block
+  constexpr int STAGES = GLU ? 4 : 3;
+  constexpr int STAGE_BYTES = KSUB * (NA * TC_A_BYTES + TC_B_BYTES);
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
@@ -185,13 +190,13 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = tmem_slot;
-  const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+  const int kblocks = (a.K + KSUB * TC_BK - 1) / (KSUB * TC_BK);
   const int wtiles = (a.n_out + TC_BM - 1) / TC_BM;
   const int total = a.tiles_y * wtiles;
 
   if (warp == 0) {
     if (lane == 0) {
-      const unsigned tx = (GLU ? 2 : 1) * TC_A_BYTES + (unsigned)ntok * TC_BK * 2;
+      const unsigned tx = KSUB * (NA * TC_A_BYTES + (unsigned)ntok * TC_BK * 2);
       long long issued = 0;           // k-blocks issued so far, over all tiles
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
@@ -208,11 +213,16 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
             ok = false;
             break;
           }
-          unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
           mbar_expect_tx(&full_bar[s], tx);
-          tma_load_3d(st, &tm_w, kb * TC_BK, n0, e, &full_bar[s]);
-          if (GLU) tma_load_3d(st + TC_A_BYTES, &tm_w, kb * TC_BK, a.n_out + n0, e, &full_bar[s]);
-          tma_load_2d(st + (GLU ? 2 : 1) * TC_A_BYTES, &tm_x, kb * TC_BK, row0, &full_bar[s]);
+#pragma unroll
+          for (int sub = 0; sub < KSUB; ++sub) {
+            // a k-block past K is all zero fill and still counts its bytes
+            unsigned char* st = tiles + (size_t)s * STAGE_BYTES + sub * (NA * TC_A_BYTES + TC_B_BYTES);
+            const int k = (kb * KSUB + sub) * TC_BK;
+            tma_load_3d(st, &tm_w, k, n0, e, &full_bar[s]);
+            if (GLU) tma_load_3d(st + TC_A_BYTES, &tm_w, k, a.n_out + n0, e, &full_bar[s]);
+            tma_load_2d(st + NA * TC_A_BYTES, &tm_x, k, row0, &full_bar[s]);
+          }
         }
       }
       if (gave_up) {
@@ -252,14 +262,17 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
             break;
           }
           tc_fence_after();
-          const unsigned st = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-          const unsigned sb = st + (GLU ? 2 : 1) * TC_A_BYTES;
 #pragma unroll
-          for (int kk = 0; kk < TC_BK / 16; ++kk) {
-            const unsigned acc = (kb | kk) != 0;
-            const unsigned long long bdesc = sw128_desc(sb + kk * 32);
-            tc_mma(tmem_d, sw128_desc(st + kk * 32), bdesc, idesc, acc);
-            if (GLU) tc_mma(tmem_d + ntok, sw128_desc(st + TC_A_BYTES + kk * 32), bdesc, idesc, acc);
+          for (int sub = 0; sub < KSUB; ++sub) {
+            const unsigned st = smem_u32(tiles + (size_t)s * STAGE_BYTES + sub * (NA * TC_A_BYTES + TC_B_BYTES));
+            const unsigned sb = st + NA * TC_A_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < TC_BK / 16; ++kk) {
+              const unsigned acc = (kb | sub | kk) != 0;
+              const unsigned long long bdesc = sw128_desc(sb + kk * 32);
+              tc_mma(tmem_d, sw128_desc(st + kk * 32), bdesc, idesc, acc);
+              if (GLU) tc_mma(tmem_d + ntok, sw128_desc(st + TC_A_BYTES + kk * 32), bdesc, idesc, acc);
+            }
           }
           tc_commit(&empty_bar[s]);
         }
@@ -463,7 +476,7 @@ int ft_moe_gemm_tc(const void* map_w, const void* map_x, void* C, long long ldc,
     }
     moe_gemm_tc_kernel<true><<<grid, 192, smem, stream>>>(mw, mx, a);
   } else {
-    const size_t smem = 6 * (TC_A_BYTES + TC_B_BYTES) + 1024;
+    const size_t smem = 3 * 2 * (TC_A_BYTES + TC_B_BYTES) + 1024;
     static bool configured = false;
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
