@@ -274,11 +274,33 @@ __device__ __forceinline__ float sumsq8(const Chunk8& c) {
   return s;
 }
 
-__global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
-  pdl_wait();
+// Sum of two values over the block in one round; every thread gets both.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch /* 66 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  __syncthreads();
+  if (lane == 0) { scratch[warp] = a; scratch[33 + warp] = b; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float sa = 0.f, sb = 0.f;
+    for (int w = 0; w < nwarps; ++w) { sa += scratch[w]; sb += scratch[33 + w]; }
+    scratch[32] = sa;
+    scratch[65] = sb;
+  }
+  __syncthreads();
+  a = scratch[32];
+  b = scratch[65];
+}
 
+// grid (tokens, parts): the blocks of a token split its heads between them;
+// with the per-layer norm every block sums the whole q and k rows itself (a
+// few KB from L2) so that no block waits for another.
+__global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
   extern __shared__ float head_inv[];
-  __shared__ float scratch[33];
+  __shared__ float scratch[66];
+  pdl_wait();
   const int t = blockIdx.x;
   const __nv_bfloat16* row = (const __nv_bfloat16*)a.qkv + (size_t)t * a.ld;
   const int d = a.d, dc = d >> 3;                 // pieces per head
@@ -288,8 +310,9 @@ __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
     float sq = 0.f, sk = 0.f;
     for (int c = threadIdx.x; c < (qn >> 3); c += blockDim.x) sq += sumsq8(load8(row + c * 8));
     for (int c = threadIdx.x; c < (kn >> 3); c += blockDim.x) sk += sumsq8(load8(row + qn + c * 8));
-    inv_q = rsqrtf(block_sum(sq, scratch) / (float)qn + a.eps);
-    inv_k = rsqrtf(block_sum(sk, scratch) / (float)kn + a.eps);
+    block_sum2(sq, sk, scratch);
+    inv_q = rsqrtf(sq / (float)qn + a.eps);
+    inv_k = rsqrtf(sk / (float)kn + a.eps);
   } else if (a.norm_mode == 2) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     for (int h = warp; h < a.nq + a.nkv; h += nwarps) {
@@ -317,7 +340,10 @@ __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
   const size_t head_stride_cache = (size_t)a.P * d;
   const int per_head = dc - hc;                   // work items per head
   const int total_q = a.nq * per_head, total = total_q + a.nkv * per_head;
-  for (int w = threadIdx.x; w < total; w += blockDim.x) {
+  // this block's share of the work items and of the V pieces
+  const int parts = gridDim.y, part = blockIdx.y;
+  const int w_begin = (int)((long long)total * part / parts), w_end = (int)((long long)total * (part + 1) / parts);
+  for (int w = w_begin + threadIdx.x; w < w_end; w += blockDim.x) {
     const bool is_q = w < total_q;
     const int ww = is_q ? w : w - total_q;
     const int h = ww / per_head, ci = ww % per_head;
@@ -360,7 +386,9 @@ __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
   }
   if (vo) {
     const __nv_bfloat16* v = row + qn + kn;
-    for (int c = threadIdx.x; c < (kn >> 3); c += blockDim.x) {
+    const int vc = kn >> 3;
+    const int v_begin = (int)((long long)vc * part / parts), v_end = (int)((long long)vc * (part + 1) / parts);
+    for (int c = v_begin + threadIdx.x; c < v_end; c += blockDim.x) {
       const int h = (c * 8) / d, i = (c * 8) % d;
       *reinterpret_cast<uint4*>(vo + (size_t)h * head_stride_cache + i) =
           *reinterpret_cast<const uint4*>(v + c * 8);
@@ -445,7 +473,12 @@ int ft_qk_rope_store(const void* qkv, void* q_out, void* kv_pages, const float* 
                        !((uintptr_t)kv_pages & 15) && !(ld & 7) && !(page_stride & 7) &&
                        !(kv_stride & 7);
   if (dtype == FT_DTYPE_BF16 && aligned && !(d & 7) && !(R & 15) && !interleaved) {
-    launch_pdl(qk_rope_store_vec_kernel, dim3(T), dim3(256), smem, stream, a);
+    // few tokens: several blocks per token share its heads
+    const int pieces = (nq + 2 * nkv) * (d >> 3);
+    int parts = T >= 512 ? 1 : (pieces + 255) / 256;
+    if (parts > 8) parts = 8;
+    if (parts < 1) parts = 1;
+    launch_pdl(qk_rope_store_vec_kernel, dim3(T, parts), dim3(256), smem, stream, a);
     FT_LAUNCH_CHECK();
     return FT_OK;
   }
