@@ -70,7 +70,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "200"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -155,7 +155,7 @@ def reference_unavailable() -> str:
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="bench.py")
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=64)
+    p.add_argument("--steps", type=int, default=256)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
@@ -263,10 +263,12 @@ def main(argv: Optional[List[str]] = None) -> int:
         engine.step([StepEntry(r, [int(t)], [0]) for r, t in zip(ids, toks)], probe=probe)
         touched = probe.get("experts_touched", [])
         ops.reset_launch_count()
+        ctx_before = engine.length(ids[0])
         with ClockSampler() as clocks:
             ms = timed(decode_once, a.steps)
         launches = ops.launch_count()
-        ctx_now = engine.length(ids[0])
+        # contexts grow by one token per step: bytes at the middle of the timed region
+        ctx_now = (ctx_before + engine.length(ids[0])) // 2
         nbytes = step_bytes(cfg, layers, batch, ctx_now, touched)
         results[batch] = {"ms": ms, "tok_s": batch / (ms / 1e3), "bytes": nbytes,
                           "gbs": nbytes / (ms / 1e3) / 1e9}
