@@ -47,9 +47,22 @@ TINY_C: Dict = dict(
     routed_scaling_factor=2.0, hidden_act="silu", vocab_size=500, tie_word_embeddings=False,
 )
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 0, "B": 1, "C": 2}
-PAGE = {"A": 4, "B": 8, "C": 16}
+# Awkward sizes on purpose: a width and a vocabulary that are no power of two,
+# one query head per KV head, a head size of 48 with 20 rotary dims, every
+# expert chosen for every token, an expert width that is no multiple of 16.
+TINY_D: Dict = dict(
+    architectures=["MiniMaxM3ForCausalLM"], model_type="minimax_m3",
+    hidden_size=200, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5,
+    head_dim=48, rotary_dim=20, rope_theta=123456.0, max_position_embeddings=300,
+    rms_norm_eps=3e-6, use_gemma_norm=False, use_qk_norm=True, qk_norm_type="per_head",
+    num_local_experts=5, num_experts_per_tok=5, intermediate_size=40,
+    scoring_func="sigmoid", use_routing_bias=False, norm_topk_prob=False,
+    routed_scaling_factor=0.5, hidden_act="silu", vocab_size=333, tie_word_embeddings=True,
+)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+PAGE = {"A": 4, "B": 8, "C": 16, "D": 32}
 
 
 def random_options(which: str):
@@ -57,6 +70,8 @@ def random_options(which: str):
     if which == "A":
         return RandomOptions(norm_std=0.0, router_bias_std=0.01)
     if which == "B":
+        return RandomOptions(norm_std=0.1)
+    if which == "D":
         return RandomOptions(norm_std=0.1)
     return RandomOptions(norm_std=0.05, router_bias_std=0.05)
 
