@@ -1,0 +1,410 @@
+// Prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM), K and
+// V pages brought in by TMA straight from the paged cache.
+//
+// A CTA owns 128 query tokens of one segment and one query head and walks the
+// key tiles (64 keys, one TMA box per 64 head dims, through the block table)
+// from key 0 to the tile's diagonal:
+//
+//   S[128 q, 64 keys]  = Q K^T      tcgen05.mma, Q and K both K-major from shared
+//                                    memory, accumulator in TMEM
+//   softmax            : a thread owns one query row (one TMEM lane): tcgen05.ld
+//                        the row, scale, mask by absolute position, running max
+//                        and sum in float32, P rounded to bfloat16 and written
+//                        back to shared memory in the swizzled K-major layout
+//   O[128 q, d]       += P V        tcgen05.mma, P K-major, V MN-major (the cache
+//                                    keeps keys as rows), accumulator in TMEM;
+//                                    when a row's max grows the softmax threads
+//                                    rescale O in TMEM before the product
+//
+//   warp 0     TMA producer (Q once; K, V tiles into a ring of two stages)
+//   warp 1     TMEM allocation; one thread issues the MMAs and commits
+//   warps 2-5  softmax and the final normalise + store
+// Two CTAs fit an SM (96 KB of shared memory and 256 TMEM columns each at head
+// size 128), so one CTA's softmax runs under the other's products.  P is written
+// over the K tile it came from (free once S is complete) when that tile is
+// large enough.
+//
+// Every mbarrier wait is bounded (about two seconds): on expiry the CTA writes
+// a code into `status`, stops issuing work, frees its TMEM and returns.
+//
+// Reference: tiled extend kernel over cached prefix + fresh keys,
+// python/freetoken/kernel/triton/attention.py:469-758 (tile 128x64, P cast to
+// bf16 at :573); mask and scale :74,118-139.
+#include <cuda.h>
+
+#include <cstring>
+
+#include "common.cuh"
+#include "mma_utils.cuh"
+#include "tcgen05.cuh"
+
+namespace ft {
+
+constexpr int AQ = 128;    // query rows per CTA (UMMA M)
+constexpr int AK = 64;     // keys per tile (UMMA N of S, K extent of P V)
+
+struct PrefillTcArgs {
+  __nv_bfloat16* out;        // [T, nq*d]
+  const int* tile_seg;       // [tiles] segment of each 64-token query tile
+  const int* tile_q0;        // [tiles] first token of the tile inside its segment
+  const int* seg_q_start;    // [S+1]
+  const int* seg_pos0;       // [S]
+  const int* block_table;    // [S, table_width]
+  int* status;
+  int nq, nkv, P, table_width;
+  float scale_log2;          // sm_scale * log2(e)
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q,
+                                                                 const __grid_constant__ CUtensorMap tm_kv,
+                                                                 PrefillTcArgs a) {
+  constexpr int NB = D / 64;                 // 64-wide (128-byte) blocks per head
+  constexpr int QB = AQ * 128;               // bytes of one block of Q
+  constexpr int KB = AK * 128;               // bytes of one block of K or V
+  constexpr int Q_BYTES = NB * QB, K_BYTES = NB * KB;
+  constexpr int P_BYTES = AQ * AK * 2;
+  constexpr bool P_IN_K = K_BYTES >= P_BYTES;
+  constexpr int STAGE = 2 * K_BYTES;
+  constexpr unsigned TMEM_COLS = D + AK <= 128 ? 128u : 256u;
+
+  // the host lists 64-token tiles; a CTA takes an even one together with its successor
+  const int tile_index = gridDim.x - 1 - blockIdx.x;     // backwards: most keys first
+  const int q0 = a.tile_q0[tile_index];
+  if (q0 % AQ) return;
+  const int seg = a.tile_seg[tile_index];
+
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* sQ = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  unsigned char* sKV = sQ + Q_BYTES;                       // [2][K | V]
+  unsigned char* sPx = sKV + 2 * STAGE;                    // only when P does not fit a K tile
+  __shared__ __align__(8) unsigned long long q_full, kv_full[2], kv_empty[2], s_full, p_full, o_done;
+  __shared__ unsigned tmem_slot;
+  __shared__ volatile int gave_up;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int kvh = head / (a.nq / a.nkv);
+  const int seg_begin = a.seg_q_start[seg];
+  const int n = a.seg_q_start[seg + 1] - seg_begin;
+  const int rows = min(AQ, n - q0);
+  const int tok0 = seg_begin + q0;
+  const int pos_first = a.seg_pos0[seg] + q0;
+  const int ntiles = (pos_first + rows - 1) / AK + 1;
+
+  if (threadIdx.x == 0) {
+    gave_up = 0;
+    mbar_init(&q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(&s_full, 1);
+    mbar_init(&p_full, 4);
+    mbar_init(&o_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = tmem_slot;
+  const unsigned tmem_o = tmem_base, tmem_s = tmem_base + D;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, Q_BYTES);
+#pragma unroll
+      for (int h = 0; h < NB; ++h) tma_load_2d(sQ + h * QB, &tm_q, head * D + h * 64, tok0, &q_full);
+      const int* table = a.block_table + (size_t)seg * a.table_width;
+      int issued = 0;
+      for (int j = 0; j < ntiles; ++j, ++issued) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], (((unsigned)j >> 1) & 1u) ^ 1u, &gave_up)) {
+          atomicCAS(a.status, 0, 11);
+          gave_up = 1;
+          break;
+        }
+        const int key0 = j * AK;
+        const int page = table[key0 / a.P], off = key0 % a.P;
+        unsigned char* sK = sKV + s * STAGE;
+        mbar_expect_tx(&kv_full[s], 2 * K_BYTES);
+#pragma unroll
+        for (int h = 0; h < NB; ++h) {
+          tma_load_5d(sK + h * KB, &tm_kv, h * 64, off, kvh, page, 0, &kv_full[s]);
+          tma_load_5d(sK + K_BYTES + h * KB, &tm_kv, h * 64, off, kvh, page, 1, &kv_full[s]);
+        }
+      }
+      if (gave_up) {
+        // let copies already in flight land before the CTA (and its shared memory) goes away
+        const unsigned long long start = global_ns();
+        while (!mbar_try(&q_full, 0) && global_ns() - start < 100000000ull) {}
+        for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j) {
+          const unsigned long long t0 = global_ns();
+          while (!mbar_try(&kv_full[j & 1], ((unsigned)j >> 1) & 1u) && global_ns() - t0 < 100000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptors: D f32, A/B bf16, M = 128; S: N = 64, both K-major;
+      // O: N = D, B (= V) MN-major
+      const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AK >> 3) << 17) |
+                               ((unsigned)(AQ >> 4) << 24);
+      const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) |
+                               ((unsigned)(AQ >> 4) << 24);
+      bool ok = mbar_wait(&q_full, 0, &gave_up);
+      if (!ok) { atomicCAS(a.status, 0, 12); gave_up = 1; }
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_full[s], ((unsigned)j >> 1) & 1u, &gave_up)) {
+          atomicCAS(a.status, 0, 13);
+          gave_up = 1;
+          break;
+        }
+        tc_fence_after();
+        const unsigned sQa = smem_u32(sQ), sK = smem_u32(sKV + s * STAGE), sV = sK + K_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          tc_mma(tmem_s, sw128_desc(sQa + (kk >> 2) * QB + (kk & 3) * 32),
+                 sw128_desc(sK + (kk >> 2) * KB + (kk & 3) * 32), idesc_s, kk > 0);
+        tc_commit(&s_full);
+        if (!mbar_wait(&p_full, (unsigned)j & 1u, &gave_up)) {
+          atomicCAS(a.status, 0, 14);
+          gave_up = 1;
+          break;
+        }
+        tc_fence_after();
+        const unsigned sP = P_IN_K ? sK : smem_u32(sPx);
+#pragma unroll
+        for (int kk = 0; kk < AK / 16; ++kk)
+          tc_mma(tmem_o, sw128_desc(sP + kk * 32), sw128_mn_desc(sV + kk * 16 * 128, KB, 1024), idesc_o,
+                 (j | kk) != 0);
+        tc_commit(&kv_empty[s]);
+        if (j == ntiles - 1) tc_commit(&o_done);
+      }
+    }
+  } else {
+    // softmax: TMEM lane = query row; this warp may touch lanes 32*(warp%4) .. +31
+    const int lane_base = (warp & 3) * 32;
+    const int r = lane_base + lane;
+    const int my_pos = pos_first + r;
+    const unsigned lane_bits = (unsigned)lane_base << 16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      ok = mbar_wait(&s_full, (unsigned)j & 1u, &gave_up);
+      if (!ok && lane == 0) { atomicCAS(a.status, 0, 15); gave_up = 1; }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      unsigned lo[32], hi[32];
+      tc_ld32(tmem_s + lane_bits, lo);
+      tc_ld32(tmem_s + lane_bits + 32, hi);
+      tc_ld_wait();
+      const int key0 = j * AK;
+      if (key0 + AK - 1 > pos_first) {
+        // a tile on the diagonal: keys after the row's own position do not count
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (key0 + c > my_pos) lo[c] = 0xff800000u;
+          if (key0 + 32 + c > my_pos) hi[c] = 0xff800000u;
+        }
+      }
+      float raw = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) raw = fmaxf(raw, fmaxf(__uint_as_float(lo[c]), __uint_as_float(hi[c])));
+      // The running max only moves when it would grow by more than 2^8: below
+      // that exp2(s - max) stays far inside float32 and bfloat16 range, and the
+      // round trip of O through registers is saved.  The softmax is the same
+      // function of the scores whichever offset is subtracted.
+      const float cand = raw * a.scale_log2;
+      const float m_new = cand > m + 8.f ? cand : m;
+      if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
+        // s_full was committed after this tile's S product, which was issued after
+        // the previous tile's O product: O is at rest
+        const float alpha = fast_exp2(m - m_new);
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          unsigned o[32];
+          tc_ld32(tmem_o + lane_bits + c0, o);
+          tc_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+          tc_st32(tmem_o + lane_bits + c0, o);
+        }
+        tc_st_wait();
+        l *= alpha;
+      }
+      m = m_new;
+      // P = exp2(s * scale - max), summed in float32, rounded to bfloat16 into the swizzled K-major tile
+      unsigned char* prow = (P_IN_K ? sKV + (j & 1) * STAGE : sPx) + (r >> 3) * 1024 + (r & 7) * 128;
+      const float neg_m = -m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        unsigned w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c = ch * 8 + 2 * i;     // keys c, c+1 of the tile
+          const float s0 = __uint_as_float(c < 32 ? lo[c] : hi[c - 32]);
+          const float s1 = __uint_as_float(c + 1 < 32 ? lo[c + 1] : hi[c + 1 - 32]);
+          const float p0 = fast_exp2(fmaf(s0, a.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(s1, a.scale_log2, neg_m));
+          sum += p0 + p1;
+          w[i] = pack_bf16(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      l += sum;
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
+    }
+    if (ok) {
+      ok = mbar_wait(&o_done, 0, &gave_up);
+      if (!ok && lane == 0) { atomicCAS(a.status, 0, 17); gave_up = 1; }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = a.out + ((size_t)(tok0 + r) * a.nq + head) * D;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        unsigned o[32];
+        tc_ld32(tmem_o + lane_bits + c0, o);
+        tc_ld_wait();
+        if (r < rows) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c0 + c) = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+template <int D>
+int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const PrefillTcArgs& a, int tiles,
+                      cudaStream_t stream) {
+  constexpr int NB = D / 64;
+  constexpr int K_BYTES = NB * AK * 128;
+  constexpr bool P_IN_K = K_BYTES >= AQ * AK * 2;
+  const size_t smem = (size_t)NB * AQ * 128 + 4 * K_BYTES + (P_IN_K ? 0 : AQ * AK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(tiles, a.nq);
+  attn_prefill_tc_kernel<D><<<grid, 192, smem, stream>>>(mq, mkv, a);
+  return FT_OK;
+}
+
+}  // namespace ft
+
+using namespace ft;
+
+extern "C" {
+
+// Tensor map over the bfloat16 query rows [rows, cols] (row stride in elements):
+// boxes of 128 rows by 64 columns in the 128-byte swizzle.  `out` receives 128 bytes.
+int ft_attn_tc_q_map(void* out, const void* base, long long rows, long long cols, long long row_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -201;
+  if ((cols & 7) || (row_stride & 7) || ((uintptr_t)base & 15)) return FT_ERR_SHAPE;
+  CUtensorMap map;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+  cuuint32_t box[2] = {64, AQ};
+  cuuint32_t es[2] = {1, 1};
+  CUresult rc = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return -202;
+  memcpy(out, &map, sizeof(map));
+  return FT_OK;
+}
+
+// Tensor map over one layer's pages, bfloat16 [2, pages, nkv, P, d] with the
+// given strides (elements) of the three outer dimensions: boxes of 64 keys by
+// 64 head dims of one page, one head, K or V.
+int ft_attn_tc_kv_map(void* out, const void* base, long long pages, long long nkv, long long P, long long d,
+                      long long head_stride, long long page_stride, long long kv_stride) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -201;
+  if ((d & 63) || P < AK || (head_stride & 7) || (page_stride & 7) || (kv_stride & 7) || ((uintptr_t)base & 15))
+    return FT_ERR_SHAPE;
+  CUtensorMap map;
+  cuuint64_t dims[5] = {(cuuint64_t)d, (cuuint64_t)P, (cuuint64_t)nkv, (cuuint64_t)pages, 2};
+  cuuint64_t strides[4] = {(cuuint64_t)d * 2, (cuuint64_t)head_stride * 2, (cuuint64_t)page_stride * 2,
+                           (cuuint64_t)kv_stride * 2};
+  cuuint32_t box[5] = {64, AK, 1, 1, 1};
+  cuuint32_t es[5] = {1, 1, 1, 1, 1};
+  CUresult rc = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, (void*)base, dims, strides, box, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return -202;
+  memcpy(out, &map, sizeof(map));
+  return FT_OK;
+}
+
+// bfloat16; head_dim 64 or 128; page size a multiple of 64; no window.
+// tile_seg / tile_q0 list the query tiles (64 tokens) of the segments to
+// process; a CTA takes an even tile with its successor.
+int ft_attn_prefill_tc(const void* map_q, const void* map_kv, void* out, const int* tile_seg,
+                       const int* tile_q0, const int* seg_q_start, const int* seg_pos0,
+                       const int* block_table, int* status, int nq, int nkv, int d, int P,
+                       int table_width, int tiles, float scale, cudaStream_t stream) {
+  if (tiles <= 0) return FT_OK;
+  if (nkv <= 0 || nq % nkv || P % AK) return FT_ERR_SHAPE;
+  CUtensorMap mq, mkv;
+  memcpy(&mq, map_q, sizeof(mq));
+  memcpy(&mkv, map_kv, sizeof(mkv));
+  PrefillTcArgs a{(__nv_bfloat16*)out, tile_seg, tile_q0, seg_q_start, seg_pos0, block_table, status,
+                  nq, nkv, P, table_width, scale * 1.4426950408889634f};
+  int rc;
+  switch (d) {
+    case 64: rc = launch_prefill_tc<64>(mq, mkv, a, tiles, stream); break;
+    case 128: rc = launch_prefill_tc<128>(mq, mkv, a, tiles, stream); break;
+    default: return FT_ERR_SHAPE;
+  }
+  if (rc != FT_OK) return rc;
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+}  // extern "C"

@@ -42,9 +42,10 @@ LIBRARIES: Dict[str, str] = {
     "skinny_gemm": "skinny_gemm.cu",
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
+    "attention_prefill_tc": "attention_prefill_tc.cu",
     "moe_gemm_tc": "moe_gemm_tc.cu",
 }
-HEADERS: List[str] = ["common.cuh", "mma_utils.cuh", "sampling_static.h"]
+HEADERS: List[str] = ["common.cuh", "mma_utils.cuh", "tcgen05.cuh", "sampling_static.h"]
 EXTRA_LINK: Dict[str, List[str]] = {}
 
 

@@ -9,7 +9,8 @@ CPU or through a library in a kernel's place.
 from __future__ import annotations
 
 import ctypes
-from typing import Optional, Sequence
+import os
+from typing import Dict, Optional, Sequence
 
 import torch
 
@@ -295,8 +296,13 @@ def check_tc_status(device) -> None:
         code_ = int(_TC_STATUS[idx].item())
         if code_:
             _TC_STATUS[idx].zero_()
-            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code_, "a role")
-            raise KernelError(f"moe_gemm_tc: {role} waited on a barrier for over two seconds and gave up")
+            kernel = "attn_prefill_tc" if code_ > 10 else "moe_gemm_tc"
+            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "the MMA issuer",
+                    11: "the TMA producer", 12: "the MMA issuer", 13: "the MMA issuer",
+                    14: "the MMA issuer", 15: "the softmax warps", 16: "the softmax warps",
+                    17: "the softmax warps"}.get(code_, "a role")
+            raise KernelError(f"{kernel}: {role} waited on a barrier for over two seconds and gave up "
+                              f"(code {code_})")
 
 
 def _tc_map(t: torch.Tensor, rows: int, K: int, row_stride: int, groups: int, box_rows: int):
@@ -474,6 +480,77 @@ def attn_prefill(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
              _ptr(seg_pos0), _ptr(block_table), kv_pages.stride(1), kv_pages.stride(0), num_heads,
              num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1], int(window or 0),
              tile_seg.numel(), float(scale), _stream()), "attn_prefill")
+
+
+# A step whose prompt portions score at least this many query-key pairs uses the
+# tcgen05 kernel (tiles of 128 queries, a pipeline of about 20 us to fill);
+# smaller ones keep the 64-query mma.sync tiles.  Measured crossover on a B200
+# at 48 heads of 128: between 256 and 512 fresh tokens, or 64 tokens on a
+# 4,096-token prefix.
+PREFILL_TC_MIN_SCORES = int(os.environ.get("FREETOKEN_PREFILL_TC_MIN_SCORES", "100000"))
+_ATTN_TC_MAPS: Dict[tuple, ctypes.Array] = {}
+
+
+def _attn_tc_map(kind: str, key: tuple, make) -> ctypes.Array:
+    m = _ATTN_TC_MAPS.get((kind,) + key)
+    if m is None:
+        if len(_ATTN_TC_MAPS) > 4096:
+            _ATTN_TC_MAPS.clear()
+        m = ctypes.create_string_buffer(128)
+        rc = make(ctypes.cast(m, ctypes.c_void_p))
+        if rc != 0:
+            raise KernelError(f"attn_prefill_tc: cannot build the {kind} tensor map (code {rc})")
+        _ATTN_TC_MAPS[(kind,) + key] = m
+    return m
+
+
+def attn_prefill_tc_takes(q: torch.Tensor, kv_pages: torch.Tensor, head_dim: int,
+                          window: Optional[int]) -> bool:
+    """bfloat16, head size 64 or 128, pages of a multiple of 64 tokens, all keys visible."""
+    return (q.dtype == torch.bfloat16 and kv_pages.dtype == torch.bfloat16 and head_dim in (64, 128)
+            and window is None and kv_pages.shape[3] % 64 == 0 and q.stride(1) == 1
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and kv_pages.data_ptr() % 16 == 0
+            and kv_pages.stride(4) == 1 and kv_pages.stride(3) == head_dim)
+
+
+def attn_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
+                    tile_seg: torch.Tensor, tile_q0: torch.Tensor, seg_q_start: torch.Tensor,
+                    seg_pos0: torch.Tensor, block_table: torch.Tensor, num_heads: int,
+                    num_kv_heads: int, head_dim: int, scale: float) -> None:
+    """Causal attention on tcgen05/TMEM with K and V pages fetched by TMA, for the
+    query tiles (64 tokens; the kernel pairs them) in ``tile_seg`` / ``tile_q0``."""
+    _need(q, "q", torch.bfloat16)
+    _need(out, "out", torch.bfloat16)
+    if not attn_prefill_tc_takes(q, kv_pages, head_dim, None) or not out.is_contiguous():
+        raise KernelError("attn_prefill_tc: refuses these tensors (bfloat16, head_dim 64/128, page % 64 == 0)")
+    for name, t in (("tile_seg", tile_seg), ("tile_q0", tile_q0), ("seg_q_start", seg_q_start),
+                    ("seg_pos0", seg_pos0), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    lib = build.load("attention_prefill_tc")
+    T, cols = q.shape
+
+    def make_q(dst):
+        f = lib.ft_attn_tc_q_map
+        f.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_longlong] * 3
+        f.restype = ctypes.c_int
+        return f(dst, q.data_ptr(), T, cols, q.stride(0))
+
+    def make_kv(dst):
+        f = lib.ft_attn_tc_kv_map
+        f.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_longlong] * 7
+        f.restype = ctypes.c_int
+        return f(dst, kv_pages.data_ptr(), kv_pages.shape[1], kv_pages.shape[2], kv_pages.shape[3],
+                 head_dim, kv_pages.stride(2), kv_pages.stride(1), kv_pages.stride(0))
+
+    map_q = _attn_tc_map("q", (q.data_ptr(), T, cols, q.stride(0)), make_q)
+    map_kv = _attn_tc_map("kv", (kv_pages.data_ptr(),) + tuple(kv_pages.shape) + tuple(kv_pages.stride()),
+                          make_kv)
+    status = tc_status(q.device)
+    f = _fn("attention_prefill_tc", "ft_attn_prefill_tc", "p p p p p p p p p i i i i i i f")
+    _check(f(ctypes.cast(map_q, ctypes.c_void_p), ctypes.cast(map_kv, ctypes.c_void_p), _ptr(out),
+             _ptr(tile_seg), _ptr(tile_q0), _ptr(seg_q_start), _ptr(seg_pos0), _ptr(block_table),
+             _ptr(status), num_heads, num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1],
+             tile_seg.numel(), float(scale), _stream()), "attn_prefill_tc")
 
 
 # ---------------------------------------------------------------- router

@@ -307,6 +307,7 @@ class Engine:
             num_decode_rows=len(dec_rows), num_prefill_rows=len(pre_rows),
             prefill_tile_seg=sec("pf_tile_seg", len(pf_tiles)),
             prefill_tile_q0=sec("pf_tile_q0", len(pf_tiles)), num_prefill_tiles=len(pf_tiles),
+            prefill_scores=sum(s.n * (s.pos0 + (s.n + 1) // 2) for s in segments if s.n > 1),
             max_decode_kv_len=(width * P if max_q == 1 else
                                max((s.pos0 + 1 for s in segments if s.n == 1), default=0)))
         in_order = N == T and rows == list(range(T))

@@ -9,7 +9,8 @@ repetitions so that no repetition finds it in L2.
 
 Kernels: ``expert_gemv`` (decode experts, weight-streaming mma.sync kernel),
 ``lm_head`` (the same kernel, dense, float32 result), ``moe_gemm_tc`` (prefill
-experts on tcgen05/TMEM with TMA), ``attn_decode``, ``attn_prefill``,
+experts on tcgen05/TMEM with TMA), ``attn_decode``, ``attn_prefill`` (mma.sync), ``attn_prefill_tc`` (tcgen05/TMEM, TMA-fed; ``_8k``: a
+8,192-token prompt),
 ``router`` (float32 router logits + top-k for a decode batch).
 """
 
@@ -122,18 +123,34 @@ def attn_decode(sets: int = 2):
     return run, B * ctx * 2 * NKV * D * 2, 4.0 * B * NQ * D * ctx, "hbm"
 
 
-def attn_prefill(sets: int = 1):
-    T = 2048
+def attn_prefill(sets: int = 1, tc: bool = False, T: int = 2048):
     kv, table = _kv(1, T, sets)
     q = torch.randn(T, NQ * D, device=DEV, dtype=torch.bfloat16)
     out = torch.empty_like(q)
     i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
     tiles = list(range(0, T, 64))
 
+    lists = (i32([0] * len(tiles)), i32(tiles), i32([0, T]), i32([0]))
+
     def run(i):
-        ops.attn_prefill(q, out, kv[0], i32([0] * len(tiles)), i32(tiles), i32([0, T]), i32([0]), table,
-                         NQ, NKV, D, D ** -0.5, None)
+        if tc:
+            ops.attn_prefill_tc(q, out, kv[0], *lists, table, NQ, NKV, D, D ** -0.5)
+        else:
+            ops.attn_prefill(q, out, kv[0], *lists, table, NQ, NKV, D, D ** -0.5, None)
     return run, 0, 4.0 * NQ * D * (T * (T + 1) / 2), "tensor"
+
+
+def attn_prefill_tc():
+    """One 2,048-token prompt, 48 heads of 128: tcgen05/TMEM with TMA-fed pages."""
+    return attn_prefill(tc=True)
+
+
+def attn_prefill_tc_8k():
+    return attn_prefill(tc=True, T=8192)
+
+
+def attn_prefill_8k():
+    return attn_prefill(T=8192)
 
 
 def router(sets: int = 8):
@@ -152,7 +169,8 @@ def router(sets: int = 8):
 
 KERNELS: Dict[str, Callable[[], Tuple[Callable[[int], None], int, float, str]]] = {
     "expert_gemv": expert_gemv, "lm_head": lm_head, "moe_gemm_tc": moe_gemm_tc,
-    "attn_decode": attn_decode, "attn_prefill": attn_prefill, "router": router,
+    "attn_decode": attn_decode, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
+    "attn_prefill_8k": attn_prefill_8k, "attn_prefill_tc_8k": attn_prefill_tc_8k, "router": router,
 }
 
 

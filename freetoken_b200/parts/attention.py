@@ -95,6 +95,8 @@ class PagedAttention(Mixer):
 
     def libraries(self, dtype) -> List[str]:
         fast = ["attention_decode", "attention_prefill"] if dtype == torch.bfloat16 else []
+        if fast and self.d in (64, 128) and self.window is None:
+            fast.append("attention_prefill_tc")
         return ["elementwise", "attention_simt"] + fast + linear.libraries(dtype)
 
     # ---- forward ----------------------------------------------------------------
@@ -126,6 +128,12 @@ class PagedAttention(Mixer):
                                 ctx.token_pos, ctx.token_seg, table, self.nq, self.nkv, self.d,
                                 self.scale, self.window, ctx.max_decode_kv_len, ctx.workspace)
             if ctx.num_prefill_tiles > 0:
+                if (ctx.prefill_scores >= ops.PREFILL_TC_MIN_SCORES
+                        and ops.attn_prefill_tc_takes(q, cache.kv_pages, self.d, self.window)):
+                    ops.attn_prefill_tc(q, o, cache.kv_pages, ctx.prefill_tile_seg, ctx.prefill_tile_q0,
+                                        ctx.seg_q_start, ctx.seg_pos0, table, self.nq, self.nkv, self.d,
+                                        self.scale)
+                    return
                 ops.attn_prefill(q, o, cache.kv_pages, ctx.prefill_tile_seg, ctx.prefill_tile_q0,
                                  ctx.seg_q_start, ctx.seg_pos0, table, self.nq, self.nkv, self.d,
                                  self.scale, self.window)

@@ -118,6 +118,8 @@ class StepContext:
     prefill_tile_seg: Optional[torch.Tensor] = None
     prefill_tile_q0: Optional[torch.Tensor] = None
     num_prefill_tiles: int = 0
+    # query-key pairs the longer segments score (n * (pos0 + n/2), summed)
+    prefill_scores: int = 0
     # when set, parts may leave measurements here (the benchmark counts the
     # experts a step touched); never set on the serving path
     probe: Optional[Dict[str, Any]] = None

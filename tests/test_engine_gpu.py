@@ -13,7 +13,8 @@ from plain_model import PlainModel
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 9, 17, 70], "B": [1, 6, 13, 31, 80], "C": [3, 40, 66, 90, 21], "D": [2, 35, 77]}
+LENGTHS = {"A": [5, 9, 17, 70], "B": [1, 6, 13, 31, 80], "C": [3, 40, 66, 90, 21], "D": [2, 35, 77],
+           "E": [2, 140, 300, 70]}
 
 
 @pytest.fixture(scope="module")
@@ -110,6 +111,28 @@ def test_cut_matches_plain(models, expected, which, dtype, cut):
         got = rd.run_engine(engine, reqs, schedule, routing)
         want = plain_logits(models, which, dtype, reqs, routing)
     compare(got, want, dtype, cut)
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+def test_tcgen05_prefill_attention_in_the_engine(models, cut, monkeypatch):
+    """Head size 64, pages of 64: every prompt portion, however short, goes
+    through the tcgen05 / TMA attention kernel (its size threshold set to 0)."""
+    from freetoken_b200.csrc import ops
+    calls = []
+    real = ops.attn_prefill_tc
+    monkeypatch.setattr(ops, "PREFILL_TC_MIN_SCORES", 0)
+    monkeypatch.setattr(ops, "attn_prefill_tc", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    which, dtype = "E", "bfloat16"
+    reqs = requests_of(which)
+    schedule = CUTS[cut](reqs)
+    page = tiny.PAGE[which]
+    engine = make_engine(models[which], dtype, page, rd.peak_tokens(schedule, page))
+    routing = {}
+    got = rd.run_engine(engine, reqs, schedule, routing)
+    ops.check_tc_status(engine.device)
+    assert calls, "the tcgen05 attention kernel never ran"
+    compare(got, plain_logits(models, which, dtype, reqs, routing), dtype, cut)
     assert engine.cache.free_pages() == engine.cache.total_pages()
 
 

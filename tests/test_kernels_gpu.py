@@ -490,3 +490,33 @@ def test_attn_prefill(nq, nkv, d, P, lens, window, standout):
                    dev([p for p, _ in lens]), table, nq, nkv, d, scale, window)
     want = _attn_ref(q, kv, pos, seg, table, nq, nkv, d, P, scale, window)
     assert torch.allclose(out.float().cpu(), want, **TOL["bfloat16"])
+
+
+# ------------------------------------------- prefill attention (tcgen05 + TMA)
+PREFILL_TC_CASES = [
+    # nq, nkv, d, P, segments (pos0, n), standout
+    (6, 1, 128, 64, [(0, 70)], None),
+    (4, 2, 128, 64, [(0, 3), (200, 130), (64, 257)], (1, 7)),      # far key, prefix in the cache
+    (5, 5, 64, 64, [(5, 128), (0, 129)], None),                     # tile edges: 128 and 129 tokens
+    (8, 2, 64, 128, [(100, 300)], (0, 2)),                          # two key tiles in a page
+    (4, 2, 128, 64, [(1000, 2), (0, 2), (0, 330)], (0, 500)),       # two-token portions beside a long one
+]
+
+
+@pytest.mark.parametrize("nq,nkv,d,P,lens,standout", PREFILL_TC_CASES)
+def test_attn_prefill_tc(nq, nkv, d, P, lens, standout):
+    o = ops()
+    q, kv, pos, seg, table = _paged_case("bfloat16", nq, nkv, d, P, lens, None, standout=standout)
+    out = torch.zeros_like(q)
+    scale = d ** -0.5
+    starts = [0]
+    for _, n in lens:
+        starts.append(starts[-1] + n)
+    tiles = [(s, q0) for s, (_, n) in enumerate(lens) for q0 in range(0, n, 64)]
+    dev = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
+    assert o.attn_prefill_tc_takes(q, kv, d, None)
+    o.attn_prefill_tc(q, out, kv, dev([t[0] for t in tiles]), dev([t[1] for t in tiles]), dev(starts),
+                      dev([p for p, _ in lens]), table, nq, nkv, d, scale)
+    o.check_tc_status(DEV)
+    want = _attn_ref(q, kv, pos, seg, table, nq, nkv, d, P, scale, None)
+    assert torch.allclose(out.float().cpu(), want, **TOL["bfloat16"])

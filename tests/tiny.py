@@ -60,9 +60,20 @@ TINY_D: Dict = dict(
     routed_scaling_factor=0.5, hidden_act="silu", vocab_size=333, tie_word_embeddings=True,
 )
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
-PAGE = {"A": 4, "B": 8, "C": 16, "D": 32}
+# Head size 64 and pages of 64 tokens: what the tcgen05 prefill attention takes.
+TINY_E: Dict = dict(
+    architectures=["MiniMaxM3ForCausalLM"], model_type="minimax_m3",
+    hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+    head_dim=64, rotary_dim=32, rope_theta=10000.0, max_position_embeddings=1024,
+    rms_norm_eps=1e-5, use_gemma_norm=False, use_qk_norm=True, qk_norm_type="per_layer",
+    num_local_experts=6, num_experts_per_tok=2, intermediate_size=48,
+    scoring_func="softmax", use_routing_bias=False, norm_topk_prob=True,
+    routed_scaling_factor=1.0, hidden_act="silu", vocab_size=320, tie_word_embeddings=False,
+)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
+PAGE = {"A": 4, "B": 8, "C": 16, "D": 32, "E": 64}
 
 
 def random_options(which: str):
@@ -71,7 +82,7 @@ def random_options(which: str):
         return RandomOptions(norm_std=0.0, router_bias_std=0.01)
     if which == "B":
         return RandomOptions(norm_std=0.1)
-    if which == "D":
+    if which in ("D", "E"):
         return RandomOptions(norm_std=0.1)
     return RandomOptions(norm_std=0.05, router_bias_std=0.05)
 
