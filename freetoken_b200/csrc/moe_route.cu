@@ -16,7 +16,7 @@ namespace ft {
 template <int WARPS>
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                      int* __restrict__ ids, float* __restrict__ weights, int T, int E,
-                                     int k, int softmax_scoring, int renormalize, float scale) {
+                                     int k, int softmax_scoring, int renormalize, float scale, int terms) {
   extern __shared__ float smem[];  // [WARPS][2][E]: scores, choice values
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_wait();
@@ -25,21 +25,32 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   if (t >= T) return;
   float* score = smem + (size_t)warp * 2 * E;
   float* choice = score + E;
-  const float* x = logits + (size_t)t * E;
+  // a row holds `terms` partial logits per expert, E apart (the router weight
+  // split into bfloat16 terms); they are summed in order, in float32
+  const float* x = logits + (size_t)t * E * terms;
+  auto logit = [&](int e) {
+    float v = x[e];
+    for (int p = 1; p < terms; ++p) v += x[p * E + e];
+    return v;
+  };
   if (softmax_scoring) {
     float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, x[e]);
+    for (int e = lane; e < E; e += 32) {
+      const float v = logit(e);
+      score[e] = v;
+      mx = fmaxf(mx, v);
+    }
     mx = warp_max(mx);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) {
-      const float p = expf(x[e] - mx);
+      const float p = expf(score[e] - mx);
       score[e] = p;
       sum += p;
     }
     sum = warp_sum(sum);
     for (int e = lane; e < E; e += 32) score[e] = score[e] / sum;
   } else {
-    for (int e = lane; e < E; e += 32) score[e] = 1.f / (1.f + expf(-x[e]));
+    for (int e = lane; e < E; e += 32) score[e] = 1.f / (1.f + expf(-logit(e)));
   }
   for (int e = lane; e < E; e += 32) choice[e] = score[e] + (bias ? bias[e] : 0.f);
   __syncwarp();
@@ -240,17 +251,17 @@ using namespace ft;
 extern "C" {
 
 int ft_router_select(const float* logits, const float* bias, int* ids, float* weights, int T,
-                     int E, int k, int softmax_scoring, int renormalize, float scale,
+                     int E, int k, int softmax_scoring, int renormalize, float scale, int terms,
                      cudaStream_t stream) {
   if (T <= 0) return FT_OK;
-  if (k <= 0 || k > E) return FT_ERR_SHAPE;
+  if (k <= 0 || k > E || terms < 1) return FT_ERR_SHAPE;
   constexpr int WARPS = 4;
   const size_t smem = (size_t)WARPS * 2 * E * sizeof(float);
   if (smem > 200 * 1024) return FT_ERR_SHAPE;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(router_select_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   launch_pdl(router_select_kernel<WARPS>, dim3((T + WARPS - 1) / WARPS), dim3(WARPS * 32), smem, stream,
-             logits, bias, ids, weights, T, E, k, softmax_scoring, renormalize, scale);
+             logits, bias, ids, weights, T, E, k, softmax_scoring, renormalize, scale, terms);
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

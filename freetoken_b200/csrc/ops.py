@@ -556,16 +556,21 @@ def attn_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
 # ---------------------------------------------------------------- router
 def router_select(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
                   weights: torch.Tensor, k: int, softmax_scoring: bool, renormalize: bool,
-                  scale: float) -> None:
+                  scale: float, terms: int = 1) -> None:
+    """Top-k of the scored router logits.  With ``terms`` > 1 a row of ``logits``
+    holds that many partial logits per expert (``[T, terms * E]``), summed in
+    order in float32 before scoring."""
     _need(logits, "logits", torch.float32)
     _need(ids, "ids", torch.int32)
     _need(weights, "weights", torch.float32)
     if bias is not None:
         _need(bias, "bias", torch.float32)
-    T, E = logits.shape
-    f = _fn("moe_route", "ft_router_select", "p p p p i i i i i f")
+    T, E = logits.shape[0], logits.shape[1] // terms
+    if logits.shape[1] != E * terms or not logits.is_contiguous():
+        raise KernelError(f"router_select: logits {tuple(logits.shape)} do not hold {terms} terms per expert")
+    f = _fn("moe_route", "ft_router_select", "p p p p i i i i i f i")
     _check(f(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(weights), T, E, k, int(softmax_scoring),
-             int(renormalize), float(scale), _stream()), "router_select")
+             int(renormalize), float(scale), int(terms), _stream()), "router_select")
 
 
 def router_logits_takes(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -31,7 +31,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Te
         if out.dtype == torch.bfloat16:
             torch.matmul(x, weight.t(), out=out)
             return out
-        if out.dtype == torch.float32 and _library_f32_out(x, weight, out):
+        if out.dtype == torch.float32 and library_f32_out(x, weight, out):
             return out
         if takes:
             ops.skinny_gemm(x, weight, out, rows_per_pass=32)
@@ -43,7 +43,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Te
 _F32_OUT = {"ok": None}
 
 
-def _library_f32_out(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
+def library_f32_out(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
     """bfloat16 x bfloat16 -> float32 through the library product, where this
     PyTorch offers it (``torch.mm(..., out_dtype=)``); the result is the
     float32 accumulator, not a rounded bfloat16."""

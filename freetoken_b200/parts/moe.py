@@ -23,6 +23,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.spec import Cat, Init, Name, Stack, TensorSpec
+from . import linear
 from .base import FeedForward, StepContext, register_feed_forward
 
 
@@ -33,6 +34,23 @@ TC_MIN_ROWS_PER_EXPERT = 8
 # Up to this many tokens the router's logits come from the one-warp-per-expert
 # kernel; above it from the tiled float32 product.
 ROUTER_SMALL_T = 64
+
+
+def bf16_terms(w: torch.Tensor) -> torch.Tensor:
+    """``[terms * E, H]`` bfloat16 whose ``terms`` row blocks sum exactly to the
+    float32 matrix ``w``: hi = bf16(w), mid = bf16(w - hi), lo = bf16(w - hi - mid)
+    (three 8-bit pieces cover a 24-bit significand; the differences are exact in
+    float32).  A product of bfloat16 activations with each term is exact in
+    float32, so a tensor-core product with float32 accumulation over the terms
+    computes the float32 router logits without rounding the weight."""
+    if w.dtype == torch.bfloat16:
+        return w
+    terms, rest = [], w.float()
+    for _ in range(3):
+        t = rest.to(torch.bfloat16)
+        terms.append(t)
+        rest = rest - t.float()
+    return torch.cat(terms, 0).contiguous()
 
 
 @register_feed_forward("routed_experts")
@@ -66,7 +84,7 @@ class RoutedExperts(FeedForward):
         self.n_gate_up = f"{self.scope}.{names['gate_up']}"
         self.n_down = f"{self.scope}.{names['down']}"
         self._each = {key: f"{self.scope}.{names[key]}" for key in ("gate", "up", "down_each")}
-        self.w_router = self.w_bias = self.w_gate_up = self.w_down = None
+        self.w_router = self.w_router_terms = self.w_bias = self.w_gate_up = self.w_down = None
 
     def tensor_specs(self) -> List[TensorSpec]:
         E, I, H = self.E, self.inter, self.hidden
@@ -85,6 +103,7 @@ class RoutedExperts(FeedForward):
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype) -> None:
         self.w_router = tensors[self.n_router]
+        self.w_router_terms = bf16_terms(self.w_router) if dtype == torch.bfloat16 else None
         self.w_bias = tensors.get(self.n_bias) if self.use_bias else None
         self.w_gate_up = tensors[self.n_gate_up]
         self.w_down = tensors[self.n_down]
@@ -99,14 +118,22 @@ class RoutedExperts(FeedForward):
         T = x.shape[0]
         ws = ctx.workspace
         logits = ws.get("moe.logits", (T, self.E), torch.float32)
+        terms = 1
         if ctx.dtype == torch.bfloat16 and T <= ROUTER_SMALL_T and ops.router_logits_takes(x, self.w_router):
             ops.router_logits(x, self.w_router, logits)
+        elif ctx.dtype == torch.bfloat16 and self.w_router_terms is not None and linear.library_f32_out(
+                x, self.w_router_terms, ws.get("moe.logit_terms", (T, self.w_router_terms.shape[0]),
+                                               torch.float32)):
+            # many rows: tensor-core products of the bfloat16 activations with the exact
+            # bfloat16 terms of the float32 router weight; the terms are summed by the selection
+            terms = self.w_router_terms.shape[0] // self.E
+            logits = ws.get("moe.logit_terms", (T, self.w_router_terms.shape[0]), torch.float32)
         else:
             ops.gemm_rows(x, self.w_router, logits)
         ids = ws.get("moe.ids", (T, self.k), torch.int32)
         weights = ws.get("moe.weights", (T, self.k), torch.float32)
         ops.router_select(logits, self.w_bias, ids, weights, self.k, self.softmax, self.renorm,
-                          self.scale)
+                          self.scale, terms)
         return ids, weights
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:

@@ -358,6 +358,35 @@ def test_router_select(E, k, softmax, renorm, use_bias, scale):
         assert ids[0].tolist() == list(range(k))
 
 
+@pytest.mark.parametrize("T,E,H", [(70, 6, 128), (300, 256, 3072), (129, 37, 200)])
+def test_router_logits_from_bf16_terms(T, E, H):
+    """The float32 router weight split into three bfloat16 terms: the terms sum
+    to the weight exactly, and tensor-core products of bfloat16 activations with
+    them, summed by the selection kernel, give the float32 logits."""
+    from freetoken_b200.parts import linear
+    from freetoken_b200.parts.moe import bf16_terms
+    x = rnd(T, H, dtype=torch.bfloat16, seed=1)
+    w = rnd(E, H, seed=2, scale=0.05)
+    terms = bf16_terms(w)
+    assert terms.shape == (3 * E, H) and terms.dtype == torch.bfloat16
+    assert torch.equal(terms.float().view(3, E, H).sum(0), w)
+    parts = torch.empty(T, 3 * E, device=DEV)
+    if not linear.library_f32_out(x, terms, parts):
+        pytest.skip("this PyTorch has no bfloat16 product with a float32 result")
+    want = x.double() @ w.double().t()
+    got = parts.view(T, 3, E).sum(1)
+    assert torch.allclose(got.double(), want, atol=2e-5, rtol=1e-5)
+    # the selection sums the terms itself
+    k = min(4, E)
+    ids = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    wts = torch.empty(T, k, device=DEV)
+    ops().router_select(parts, None, ids, wts, k, False, True, 1.0, terms=3)
+    ids2 = torch.empty_like(ids)
+    wts2 = torch.empty_like(wts)
+    ops().router_select(got.contiguous(), None, ids2, wts2, k, False, True, 1.0)
+    assert torch.equal(ids, ids2) and torch.allclose(wts, wts2, atol=1e-6)
+
+
 @pytest.mark.parametrize("E,k,T", [(4, 2, 1), (8, 3, 50), (256, 8, 300), (5, 1, 64)])
 def test_moe_sort_is_stable_counting_sort(E, k, T):
     ids, want_route, want_token, want_off = _grouped_case(E, k, T, seed=3)
