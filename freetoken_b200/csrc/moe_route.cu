@@ -244,6 +244,114 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
   }
 }
 
+
+// ---- the same sort for many routes (prompt portions): chunks of 256 routes
+// Three launches instead of one warp per expert walking every route:
+//   1. per chunk, a histogram over the experts        -> chunk_counts[c][e]
+//   2. per expert, the running sum over the chunks    -> chunk_counts[c][e] =
+//      routes of e before chunk c; counts, offsets and the active list
+//   3. per chunk (one warp), routes are ranked 32 at a time: lanes with the
+//      same expert find each other with match.any, a lane's rank is the number
+//      of lower lanes among them, the expert's cursor then moves on
+// The result is the same stable order (ascending route inside an expert).
+constexpr int SORT_CHUNK = 256;
+
+__global__ void __launch_bounds__(SORT_CHUNK) moe_chunk_count_kernel(const int* __restrict__ ids,
+                                                                    int* __restrict__ chunk_counts, int R,
+                                                                    int E) {
+  extern __shared__ int hist[];   // [E]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int r = blockIdx.x * SORT_CHUNK + threadIdx.x;
+  if (r < R) {
+    const int e = ids[r];
+    if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_counts[(size_t)blockIdx.x * E + e] = hist[e];
+}
+
+// One block.  Experts are taken blockDim at a time, in ascending order, with a
+// carry for the offsets and for the number of busy experts.
+__global__ void __launch_bounds__(1024) moe_chunk_scan_kernel(int* __restrict__ chunk_counts,
+                                                              int* __restrict__ counts, int* __restrict__ offsets,
+                                                              int* __restrict__ active, int chunks, int E) {
+  __shared__ int scan_rows[1024], scan_busy[1024];
+  __shared__ int carry_rows, carry_busy;
+  if (threadIdx.x == 0) { carry_rows = 0; carry_busy = 0; }
+  __syncthreads();
+  for (int base = 0; base < E; base += blockDim.x) {
+    const int e = base + threadIdx.x;
+    int total = 0;
+    if (e < E) {
+      for (int c = 0; c < chunks; ++c) {
+        const int v = chunk_counts[(size_t)c * E + e];
+        chunk_counts[(size_t)c * E + e] = total;
+        total += v;
+      }
+      counts[e] = total;
+    }
+    scan_rows[threadIdx.x] = total;
+    scan_busy[threadIdx.x] = total > 0;
+    __syncthreads();
+    for (int o = 1; o < (int)blockDim.x; o <<= 1) {
+      const int a = threadIdx.x >= (unsigned)o ? scan_rows[threadIdx.x - o] : 0;
+      const int b = threadIdx.x >= (unsigned)o ? scan_busy[threadIdx.x - o] : 0;
+      __syncthreads();
+      scan_rows[threadIdx.x] += a;
+      scan_busy[threadIdx.x] += b;
+      __syncthreads();
+    }
+    if (e < E) {
+      const int before = carry_rows + scan_rows[threadIdx.x] - total;
+      offsets[e] = before;
+      if (total > 0) active[carry_busy + scan_busy[threadIdx.x] - 1] = e;
+      if (e == E - 1) {
+        offsets[E] = before + total;
+        active[E] = carry_busy + scan_busy[threadIdx.x];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) {
+      carry_rows += scan_rows[threadIdx.x];
+      carry_busy += scan_busy[threadIdx.x];
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(128) moe_chunk_scatter_kernel(const int* __restrict__ ids,
+                                                                const int* __restrict__ chunk_counts,
+                                                                const int* __restrict__ offsets,
+                                                                int* __restrict__ sorted_route,
+                                                                int* __restrict__ sorted_token, int R, int E,
+                                                                int k, int chunks) {
+  extern __shared__ int cursors[];   // [warps][E]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (c >= chunks) return;
+  int* cursor = cursors + (size_t)warp * E;
+  for (int e = lane; e < E; e += 32) cursor[e] = offsets[e] + chunk_counts[(size_t)c * E + e];
+  __syncwarp();
+  const int first = c * SORT_CHUNK;
+  for (int it = 0; it < SORT_CHUNK / 32; ++it) {
+    const int r = first + it * 32 + lane;
+    int e = r < R ? ids[r] : -1;
+    if (e < 0 || e >= E) e = -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int at = 0;
+    if (e >= 0) at = cursor[e] + rank;
+    __syncwarp();
+    if (e >= 0 && rank == 0) cursor[e] += __popc(peers);
+    __syncwarp();
+    if (e >= 0) {
+      sorted_route[at] = r;
+      sorted_token[at] = r / k;
+    }
+  }
+}
+
 }  // namespace ft
 
 using namespace ft;
@@ -277,9 +385,32 @@ int ft_router_logits(const void* x, int x_dtype, long long ldx, const float* W, 
   return FT_OK;
 }
 
+// Ints of scratch the chunked sort needs for R routes over E experts.
+long long ft_moe_sort_scratch(int R, int E) {
+  return (long long)((R + SORT_CHUNK - 1) / SORT_CHUNK) * E;
+}
+
+// `scratch` (ft_moe_sort_scratch ints) selects the chunked sort; without it one
+// warp per expert walks the routes (few routes: a decode batch).
 int ft_moe_sort(const int* ids, int* counts, int* offsets, int* sorted_route, int* sorted_token,
-                int* active, int R, int E, int k, cudaStream_t stream) {
+                int* active, int* scratch, int R, int E, int k, cudaStream_t stream) {
   if (R <= 0) return FT_OK;
+  if (scratch) {
+    const int chunks = (R + SORT_CHUNK - 1) / SORT_CHUNK;
+    const size_t hist = (size_t)E * sizeof(int), cur = 4 * hist;
+    if (cur > 200 * 1024) return FT_ERR_SHAPE;
+    if (cur > 48 * 1024) {
+      cudaFuncSetAttribute(moe_chunk_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hist);
+      cudaFuncSetAttribute(moe_chunk_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cur);
+    }
+    moe_chunk_count_kernel<<<chunks, SORT_CHUNK, hist, stream>>>(ids, scratch, R, E);
+    moe_chunk_scan_kernel<<<1, E < 1024 ? ((E + 31) / 32) * 32 : 1024, 0, stream>>>(scratch, counts, offsets,
+                                                                                   active, chunks, E);
+    moe_chunk_scatter_kernel<<<(chunks + 3) / 4, 128, cur, stream>>>(ids, scratch, offsets, sorted_route,
+                                                                     sorted_token, R, E, k, chunks);
+    FT_LAUNCH_CHECK();
+    return FT_OK;
+  }
   const int warps = 4;
   const int blocks = (E + warps - 1) / warps;
   launch_pdl(moe_count_kernel, dim3(blocks), dim3(warps * 32), 0, stream, ids, counts, R, E);

@@ -594,9 +594,11 @@ def router_logits(x: torch.Tensor, w: torch.Tensor, logits: torch.Tensor) -> Non
 
 def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor,
              sorted_route: torch.Tensor, sorted_token: torch.Tensor, active: torch.Tensor,
-             num_experts: int, k: int) -> None:
+             num_experts: int, k: int, scratch: Optional[torch.Tensor] = None) -> None:
     """Stable counting sort of the ``T*k`` routes by expert; ``active`` gets the
-    experts that have routes (ascending) and, at index ``num_experts``, their number."""
+    experts that have routes (ascending) and, at index ``num_experts``, their number.
+    With ``scratch`` (int32, :func:`moe_sort_scratch` elements) the routes are
+    sorted in chunks, which is faster from a few thousand routes on."""
     for name, t in (("ids", ids), ("counts", counts), ("offsets", offsets),
                     ("sorted_route", sorted_route), ("sorted_token", sorted_token),
                     ("active", active)):
@@ -606,9 +608,24 @@ def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor,
             or sorted_route.numel() < R or sorted_token.numel() < R \
             or active.numel() < num_experts + 1:
         raise KernelError("moe_sort: output buffers are too small")
-    f = _fn("moe_route", "ft_moe_sort", "p p p p p p i i i")
+    if scratch is not None:
+        _need(scratch, "scratch", torch.int32)
+        if scratch.numel() < moe_sort_scratch(R, num_experts):
+            raise KernelError("moe_sort: the scratch buffer is too small")
+    f = _fn("moe_route", "ft_moe_sort", "p p p p p p p i i i")
     _check(f(_ptr(ids), _ptr(counts), _ptr(offsets), _ptr(sorted_route), _ptr(sorted_token),
-             _ptr(active), R, num_experts, k, _stream()), "moe_sort")
+             _ptr(active), _ptr(scratch), R, num_experts, k, _stream()), "moe_sort")
+    if scratch is not None:
+        global LAUNCHES
+        LAUNCHES += 1      # three kernels instead of two
+
+
+MOE_SORT_CHUNKED_FROM = 2048   # routes from which the chunked sort is used
+
+
+def moe_sort_scratch(routes: int, num_experts: int) -> int:
+    """int32 elements of scratch the chunked sort needs."""
+    return -(-routes // 256) * num_experts
 
 
 # -------------------------------------------------------------- sampling

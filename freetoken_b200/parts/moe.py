@@ -146,7 +146,11 @@ class RoutedExperts(FeedForward):
         sorted_route = ws.get("moe.sorted_route", (R,), torch.int32)
         sorted_token = ws.get("moe.sorted_token", (R,), torch.int32)
         active = ws.get("moe.active", (self.E + 1,), torch.int32)
-        ops.moe_sort(ids.view(-1), counts, offsets, sorted_route, sorted_token, active, self.E, self.k)
+        scratch = None
+        if R >= ops.MOE_SORT_CHUNKED_FROM:
+            scratch = ws.get("moe.sort_scratch", (ops.moe_sort_scratch(R, self.E),), torch.int32)
+        ops.moe_sort(ids.view(-1), counts, offsets, sorted_route, sorted_token, active, self.E, self.k,
+                     scratch)
         if ctx.probe is not None:
             if "router_ids" in ctx.probe:
                 ctx.probe["router_ids"].append(ids.clone())

@@ -122,6 +122,7 @@ def test_tcgen05_prefill_attention_in_the_engine(models, cut, monkeypatch):
     calls = []
     real = ops.attn_prefill_tc
     monkeypatch.setattr(ops, "PREFILL_TC_MIN_SCORES", 0)
+    monkeypatch.setattr(ops, "MOE_SORT_CHUNKED_FROM", 1)      # and the chunked route sort
     monkeypatch.setattr(ops, "attn_prefill_tc", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
     which, dtype = "E", "bfloat16"
     reqs = requests_of(which)

@@ -387,16 +387,21 @@ def test_router_logits_from_bf16_terms(T, E, H):
     assert torch.equal(ids, ids2) and torch.allclose(wts, wts2, atol=1e-6)
 
 
-@pytest.mark.parametrize("E,k,T", [(4, 2, 1), (8, 3, 50), (256, 8, 300), (5, 1, 64)])
-def test_moe_sort_is_stable_counting_sort(E, k, T):
+@pytest.mark.parametrize("chunked", [False, True])
+@pytest.mark.parametrize("E,k,T", [(4, 2, 1), (8, 3, 50), (256, 8, 300), (5, 1, 64), (37, 5, 1111),
+                                   (1500, 2, 700)])
+def test_moe_sort_is_stable_counting_sort(E, k, T, chunked):
     ids, want_route, want_token, want_off = _grouped_case(E, k, T, seed=3)
     R = T * k
+    scratch = None
+    if chunked:
+        scratch = torch.full((ops().moe_sort_scratch(R, E),), -7, dtype=torch.int32, device=DEV)
     counts = torch.empty(E, dtype=torch.int32, device=DEV)
     offsets = torch.empty(E + 1, dtype=torch.int32, device=DEV)
     sr = torch.empty(R, dtype=torch.int32, device=DEV)
     st = torch.empty(R, dtype=torch.int32, device=DEV)
     active = torch.full((E + 1,), -1, dtype=torch.int32, device=DEV)
-    ops().moe_sort(ids.view(-1), counts, offsets, sr, st, active, E, k)
+    ops().moe_sort(ids.view(-1), counts, offsets, sr, st, active, E, k, scratch)
     busy = (want_off[1:] > want_off[:-1]).nonzero().flatten().to(torch.int32)
     assert int(active[E]) == busy.numel()
     assert torch.equal(active[:busy.numel()], busy)
