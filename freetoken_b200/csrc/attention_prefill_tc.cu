@@ -10,19 +10,18 @@
 //   softmax            : a thread owns one query row (one TMEM lane): tcgen05.ld
 //                        the row, scale, mask by absolute position, running max
 //                        and sum in float32, P rounded to bfloat16 and written
-//                        back to shared memory in the swizzled K-major layout
-//   O[128 q, d]       += P V        tcgen05.mma, P K-major, V MN-major (the cache
-//                                    keeps keys as rows), accumulator in TMEM;
-//                                    when a row's max grows the softmax threads
-//                                    rescale O in TMEM before the product
+//                        back over S in TMEM (two keys per 32-bit column)
+//   O[128 q, d]       += P V        tcgen05.mma, P from TMEM, V MN-major from shared
+//                                    memory (the cache keeps keys as rows),
+//                                    accumulator in TMEM; when a row's max grows
+//                                    the softmax threads rescale O in TMEM first
 //
-//   warp 0     TMA producer (Q once; K, V tiles into a ring of two stages)
+//   warp 0     TMA producer (Q once; K and V tiles into rings of two stages each)
 //   warp 1     TMEM allocation; one thread issues the MMAs and commits
 //   warps 2-5  softmax and the final normalise + store
-// Two CTAs fit an SM (96 KB of shared memory and 256 TMEM columns each at head
-// size 128), so one CTA's softmax runs under the other's products.  P is written
-// over the K tile it came from (free once S is complete) when that tile is
-// large enough.
+// S has two TMEM buffers: the S product of tile j+1 is issued before the O
+// product of tile j, so it runs under the softmax of tile j.  Two CTAs fit an SM
+// (96 KB of shared memory and 256 TMEM columns each at head size 128).
 //
 // Every mbarrier wait is bounded (about two seconds): on expiry the CTA writes
 // a code into `status`, stops issuing work, frees its TMEM and returns.
@@ -63,10 +62,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
   constexpr int QB = AQ * 128;               // bytes of one block of Q
   constexpr int KB = AK * 128;               // bytes of one block of K or V
   constexpr int Q_BYTES = NB * QB, K_BYTES = NB * KB;
-  constexpr int P_BYTES = AQ * AK * 2;
-  constexpr bool P_IN_K = K_BYTES >= P_BYTES;
-  constexpr int STAGE = 2 * K_BYTES;
-  constexpr unsigned TMEM_COLS = D + AK <= 128 ? 128u : 256u;
+  constexpr unsigned TMEM_COLS = 256u;       // O: D columns, then S/P: 2 x 64
 
   // the host lists 64-token tiles; a CTA takes an even one together with its successor
   const int tile_index = gridDim.x - 1 - blockIdx.x;     // backwards: most keys first
@@ -76,9 +72,10 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
 
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* sQ = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  unsigned char* sKV = sQ + Q_BYTES;                       // [2][K | V]
-  unsigned char* sPx = sKV + 2 * STAGE;                    // only when P does not fit a K tile
-  __shared__ __align__(8) unsigned long long q_full, kv_full[2], kv_empty[2], s_full, p_full, o_done;
+  unsigned char* sKr = sQ + Q_BYTES;                       // K ring [2]
+  unsigned char* sVr = sKr + 2 * K_BYTES;                  // V ring [2]
+  __shared__ __align__(8) unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2],
+      p_full[2], pv_done;
   __shared__ unsigned tmem_slot;
   __shared__ volatile int gave_up;
 
@@ -95,10 +92,12 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
   if (threadIdx.x == 0) {
     gave_up = 0;
     mbar_init(&q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(&s_full, 1);
-    mbar_init(&p_full, 4);
-    mbar_init(&o_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4);
+    }
+    mbar_init(&pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -118,31 +117,51 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
 #pragma unroll
       for (int h = 0; h < NB; ++h) tma_load_2d(sQ + h * QB, &tm_q, head * D + h * 64, tok0, &q_full);
       const int* table = a.block_table + (size_t)seg * a.table_width;
-      int issued = 0;
-      for (int j = 0; j < ntiles; ++j, ++issued) {
-        const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], (((unsigned)j >> 1) & 1u) ^ 1u, &gave_up)) {
-          atomicCAS(a.status, 0, 11);
-          gave_up = 1;
-          break;
-        }
-        const int key0 = j * AK;
-        const int page = table[key0 / a.P], off = key0 % a.P;
-        unsigned char* sK = sKV + s * STAGE;
-        mbar_expect_tx(&kv_full[s], 2 * K_BYTES);
+      // K runs one tile ahead of V: K_j is wanted a whole softmax earlier than V_j
+      int k_issued = 0, v_issued = 0;
+      for (int j = 0; j <= ntiles; ++j) {
+        if (j < ntiles) {
+          const int s = j & 1;
+          if (!mbar_wait(&k_empty[s], (((unsigned)j >> 1) & 1u) ^ 1u, &gave_up)) {
+            atomicCAS(a.status, 0, 11);
+            gave_up = 1;
+            break;
+          }
+          const int key0 = j * AK;
+          const int page = table[key0 / a.P], off = key0 % a.P;
+          mbar_expect_tx(&k_full[s], K_BYTES);
 #pragma unroll
-        for (int h = 0; h < NB; ++h) {
-          tma_load_5d(sK + h * KB, &tm_kv, h * 64, off, kvh, page, 0, &kv_full[s]);
-          tma_load_5d(sK + K_BYTES + h * KB, &tm_kv, h * 64, off, kvh, page, 1, &kv_full[s]);
+          for (int h = 0; h < NB; ++h)
+            tma_load_5d(sKr + s * K_BYTES + h * KB, &tm_kv, h * 64, off, kvh, page, 0, &k_full[s]);
+          ++k_issued;
+        }
+        if (j > 0) {
+          const int i = j - 1, s = i & 1;
+          if (!mbar_wait(&v_empty[s], (((unsigned)i >> 1) & 1u) ^ 1u, &gave_up)) {
+            atomicCAS(a.status, 0, 11);
+            gave_up = 1;
+            break;
+          }
+          const int key0 = i * AK;
+          const int page = table[key0 / a.P], off = key0 % a.P;
+          mbar_expect_tx(&v_full[s], K_BYTES);
+#pragma unroll
+          for (int h = 0; h < NB; ++h)
+            tma_load_5d(sVr + s * K_BYTES + h * KB, &tm_kv, h * 64, off, kvh, page, 1, &v_full[s]);
+          ++v_issued;
         }
       }
       if (gave_up) {
         // let copies already in flight land before the CTA (and its shared memory) goes away
         const unsigned long long start = global_ns();
         while (!mbar_try(&q_full, 0) && global_ns() - start < 100000000ull) {}
-        for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j) {
+        for (int j = k_issued > 2 ? k_issued - 2 : 0; j < k_issued; ++j) {
           const unsigned long long t0 = global_ns();
-          while (!mbar_try(&kv_full[j & 1], ((unsigned)j >> 1) & 1u) && global_ns() - t0 < 100000000ull) {}
+          while (!mbar_try(&k_full[j & 1], ((unsigned)j >> 1) & 1u) && global_ns() - t0 < 100000000ull) {}
+        }
+        for (int j = v_issued > 2 ? v_issued - 2 : 0; j < v_issued; ++j) {
+          const unsigned long long t0 = global_ns();
+          while (!mbar_try(&v_full[j & 1], ((unsigned)j >> 1) & 1u) && global_ns() - t0 < 100000000ull) {}
         }
       }
     }
@@ -156,33 +175,45 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
                                ((unsigned)(AQ >> 4) << 24);
       bool ok = mbar_wait(&q_full, 0, &gave_up);
       if (!ok) { atomicCAS(a.status, 0, 12); gave_up = 1; }
-      for (int j = 0; j < ntiles && ok; ++j) {
+      const unsigned sQa = smem_u32(sQ);
+      // S product of tile j into S buffer j & 1; frees the K stage when done
+      auto issue_s = [&](int j) -> bool {
         const int s = j & 1;
-        if (!mbar_wait(&kv_full[s], ((unsigned)j >> 1) & 1u, &gave_up)) {
+        if (!mbar_wait(&k_full[s], ((unsigned)j >> 1) & 1u, &gave_up)) {
           atomicCAS(a.status, 0, 13);
           gave_up = 1;
-          break;
+          return false;
         }
         tc_fence_after();
-        const unsigned sQa = smem_u32(sQ), sK = smem_u32(sKV + s * STAGE), sV = sK + K_BYTES;
+        const unsigned sK = smem_u32(sKr + s * K_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          tc_mma(tmem_s, sw128_desc(sQa + (kk >> 2) * QB + (kk & 3) * 32),
+          tc_mma(tmem_s + (unsigned)(s * AK), sw128_desc(sQa + (kk >> 2) * QB + (kk & 3) * 32),
                  sw128_desc(sK + (kk >> 2) * KB + (kk & 3) * 32), idesc_s, kk > 0);
-        tc_commit(&s_full);
-        if (!mbar_wait(&p_full, (unsigned)j & 1u, &gave_up)) {
+        tc_commit(&s_full[s]);
+        tc_commit(&k_empty[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int s = j & 1;
+        // the next tile's S goes first: it runs under this tile's softmax.  Its buffer
+        // held P of tile j-1, read by an O product issued before it (MMAs run in order)
+        if (j + 1 < ntiles && !issue_s(j + 1)) break;
+        if (!mbar_wait(&p_full[s], ((unsigned)j >> 1) & 1u, &gave_up) ||
+            !mbar_wait(&v_full[s], ((unsigned)j >> 1) & 1u, &gave_up)) {
           atomicCAS(a.status, 0, 14);
           gave_up = 1;
           break;
         }
         tc_fence_after();
-        const unsigned sP = P_IN_K ? sK : smem_u32(sPx);
+        const unsigned sV = smem_u32(sVr + s * K_BYTES);
 #pragma unroll
         for (int kk = 0; kk < AK / 16; ++kk)
-          tc_mma(tmem_o, sw128_desc(sP + kk * 32), sw128_mn_desc(sV + kk * 16 * 128, KB, 1024), idesc_o,
-                 (j | kk) != 0);
-        tc_commit(&kv_empty[s]);
-        if (j == ntiles - 1) tc_commit(&o_done);
+          tc_mma_ts(tmem_o, tmem_s + (unsigned)(s * AK + kk * 8), sw128_mn_desc(sV + kk * 16 * 128, KB, 1024),
+                    idesc_o, (j | kk) != 0);
+        tc_commit(&v_empty[s]);
+        tc_commit(&pv_done);
       }
     }
   } else {
@@ -194,14 +225,15 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < ntiles; ++j) {
-      ok = mbar_wait(&s_full, (unsigned)j & 1u, &gave_up);
+      const unsigned tmem_sj = tmem_s + (unsigned)((j & 1) * AK) + lane_bits;
+      ok = mbar_wait(&s_full[j & 1], ((unsigned)j >> 1) & 1u, &gave_up);
       if (!ok && lane == 0) { atomicCAS(a.status, 0, 15); gave_up = 1; }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
       unsigned lo[32], hi[32];
-      tc_ld32(tmem_s + lane_bits, lo);
-      tc_ld32(tmem_s + lane_bits + 32, hi);
+      tc_ld32(tmem_sj, lo);
+      tc_ld32(tmem_sj + 32, hi);
       tc_ld_wait();
       const int key0 = j * AK;
       if (key0 + AK - 1 > pos_first) {
@@ -222,8 +254,13 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       const float cand = raw * a.scale_log2;
       const float m_new = cand > m + 8.f ? cand : m;
       if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
-        // s_full was committed after this tile's S product, which was issued after
-        // the previous tile's O product: O is at rest
+        // O must be at rest: the previous tile's O product done (the one before it
+        // is, since this tile's S product was issued after it), this tile's not issued
+        ok = mbar_wait(&pv_done, (unsigned)(j - 1) & 1u, &gave_up);
+        if (!ok && lane == 0) { atomicCAS(a.status, 0, 16); gave_up = 1; }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        tc_fence_after();
         const float alpha = fast_exp2(m - m_new);
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
@@ -238,33 +275,30 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         l *= alpha;
       }
       m = m_new;
-      // P = exp2(s * scale - max), summed in float32, rounded to bfloat16 into the swizzled K-major tile
-      unsigned char* prow = (P_IN_K ? sKV + (j & 1) * STAGE : sPx) + (r >> 3) * 1024 + (r & 7) * 128;
+      // P = exp2(s * scale - max), summed in float32, rounded to bfloat16 and written
+      // over S: column c of the buffer holds keys 2c and 2c+1
       const float neg_m = -m_new;
       float sum = 0.f;
+      unsigned pk[32];
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        unsigned w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = ch * 8 + 2 * i;     // keys c, c+1 of the tile
-          const float s0 = __uint_as_float(c < 32 ? lo[c] : hi[c - 32]);
-          const float s1 = __uint_as_float(c + 1 < 32 ? lo[c + 1] : hi[c + 1 - 32]);
-          const float p0 = fast_exp2(fmaf(s0, a.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(s1, a.scale_log2, neg_m));
-          sum += p0 + p1;
-          w[i] = pack_bf16(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int c = 0; c < 16; ++c) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(lo[2 * c]), a.scale_log2, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(lo[2 * c + 1]), a.scale_log2, neg_m));
+        const float p2 = fast_exp2(fmaf(__uint_as_float(hi[2 * c]), a.scale_log2, neg_m));
+        const float p3 = fast_exp2(fmaf(__uint_as_float(hi[2 * c + 1]), a.scale_log2, neg_m));
+        sum += (p0 + p1) + (p2 + p3);
+        pk[c] = pack_bf16(p0, p1);
+        pk[16 + c] = pack_bf16(p2, p3);
       }
+      tc_st32(tmem_sj, pk);
+      tc_st_wait();
       l += sum;
-      fence_proxy_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full);
+      if (lane == 0) mbar_arrive(&p_full[j & 1]);
     }
     if (ok) {
-      ok = mbar_wait(&o_done, 0, &gave_up);
+      ok = mbar_wait(&pv_done, (unsigned)(ntiles - 1) & 1u, &gave_up);
       if (!ok && lane == 0) { atomicCAS(a.status, 0, 17); gave_up = 1; }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }
@@ -320,8 +354,7 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const Prefi
                       cudaStream_t stream) {
   constexpr int NB = D / 64;
   constexpr int K_BYTES = NB * AK * 128;
-  constexpr bool P_IN_K = K_BYTES >= AQ * AK * 2;
-  const size_t smem = (size_t)NB * AQ * 128 + 4 * K_BYTES + (P_IN_K ? 0 : AQ * AK * 2) + 1024;
+  const size_t smem = (size_t)NB * AQ * 128 + 4 * K_BYTES + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
