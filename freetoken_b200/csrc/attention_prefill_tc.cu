@@ -244,9 +244,13 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
           if (key0 + 32 + c > my_pos) hi[c] = 0xff800000u;
         }
       }
-      float raw = -INFINITY;
+      // four independent chains each for the max and (below) the sum: two warps per
+      // scheduler cannot hide one long dependent chain
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 32; ++c) raw = fmaxf(raw, fmaxf(__uint_as_float(lo[c]), __uint_as_float(hi[c])));
+      for (int c = 0; c < 32; ++c)
+        mx4[c & 3] = fmaxf(mx4[c & 3], fmaxf(__uint_as_float(lo[c]), __uint_as_float(hi[c])));
+      const float raw = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // The running max only moves when it would grow by more than 2^8: below
       // that exp2(s - max) stays far inside float32 and bfloat16 range, and the
       // round trip of O through registers is saved.  The softmax is the same
@@ -278,7 +282,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       // P = exp2(s * scale - max), summed in float32, rounded to bfloat16 and written
       // over S: column c of the buffer holds keys 2c and 2c+1
       const float neg_m = -m_new;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       unsigned pk[32];
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
@@ -286,10 +290,11 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         const float p1 = fast_exp2(fmaf(__uint_as_float(lo[2 * c + 1]), a.scale_log2, neg_m));
         const float p2 = fast_exp2(fmaf(__uint_as_float(hi[2 * c]), a.scale_log2, neg_m));
         const float p3 = fast_exp2(fmaf(__uint_as_float(hi[2 * c + 1]), a.scale_log2, neg_m));
-        sum += (p0 + p1) + (p2 + p3);
+        sum4[c & 3] += (p0 + p1) + (p2 + p3);
         pk[c] = pack_bf16(p0, p1);
         pk[16 + c] = pack_bf16(p2, p3);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tc_st32(tmem_sj, pk);
       tc_st_wait();
       l += sum;
