@@ -8,9 +8,10 @@ random weights of the configured architecture and uniform random token ids.
 
 One JSON line is printed.  ``value`` is decode tokens/s at the main batch
 size, timed on the device around whole steps (step function + greedy
-sampling); ``e2e`` is the same through ``LLM.run_step`` - plan, pinned-host to
-device copy of the step's inputs, step, sample, device-to-host read of the
-tokens, bookkeeping.  Every step reads far more weight bytes than the L2 cache
+sampling); ``e2e`` is the same through ``LLM.run_step_overlapped``, the loop
+``LLM.generate`` runs - plan, pinned-host to device copy of the step's inputs,
+step, sample, device-to-host read of the tokens (of the step before: the next
+step is launched first), bookkeeping.  Every step reads far more weight bytes than the L2 cache
 holds, so no flush is needed between timed steps.
 """
 
@@ -290,9 +291,12 @@ def main(argv: Optional[List[str]] = None) -> int:
         rngs[("e2e", i)] = RequestRng(i)
     while llm.scheduler.pending or llm.scheduler.prefilling:
         llm.run_step(rngs)
+    # the loop generate() runs: a step is launched (its inputs copied from pinned host
+    # memory) before the tokens of the step before it are read from pinned host memory
     for _ in range(max(3, a.warmup)):
-        llm.run_step(rngs)
-    e2e_ms = timed(lambda: llm.run_step(rngs), a.steps)
+        llm.run_step_overlapped(rngs)
+    e2e_ms = timed(lambda: llm.run_step_overlapped(rngs), a.steps)
+    llm.drain()
     h2d = engine.last_meta_ints * 4
     d2h = a.batch * 4
     for r in list(llm.scheduler.running):

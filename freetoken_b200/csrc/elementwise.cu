@@ -422,11 +422,31 @@ __global__ void gather_rows_kernel(const AT* __restrict__ src, const int* __rest
   for (int i = threadIdx.x; i < H; i += blockDim.x) d[i] = s[i];
 }
 
+// ids[rows[i]] = src[src_index[i]]: the tokens a step sampled become the next
+// step's inputs without a round trip through the host.  An id outside the
+// vocabulary (which the sampler never writes) becomes 0.
+__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ rows,
+                                    const int* __restrict__ src, const int* __restrict__ src_index, int n,
+                                    int vocab) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int t = src[src_index[i]];
+  ids[rows[i]] = (t < 0 || t >= vocab) ? 0 : t;
+}
+
 }  // namespace ft
 
 using namespace ft;
 
 extern "C" {
+
+int ft_patch_tokens(int* ids, const int* rows, const int* src, const int* src_index, int n, int vocab,
+                    cudaStream_t stream) {
+  if (n <= 0) return FT_OK;
+  ft::patch_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, rows, src, src_index, n, vocab);
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
 
 int ft_embed_gather(const int* ids, const void* table, int table_dtype, float* residual, int T,
                     int H, int vocab, cudaStream_t stream) {

@@ -104,6 +104,18 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor)
              _stream()), "embed_gather")
 
 
+def patch_tokens(ids: torch.Tensor, rows: torch.Tensor, src: torch.Tensor, src_index: torch.Tensor,
+                 vocab: int) -> None:
+    """ids[rows[i]] = src[src_index[i]] (all int32, on the device)."""
+    for name, t in (("ids", ids), ("rows", rows), ("src", src), ("src_index", src_index)):
+        _need(t, name, torch.int32)
+    if rows.numel() != src_index.numel():
+        raise KernelError("patch_tokens: rows and src_index differ in length")
+    f = _fn("elementwise", "ft_patch_tokens", "p p p p i i")
+    _check(f(_ptr(ids), _ptr(rows), _ptr(src), _ptr(src_index), rows.numel(), vocab, _stream()),
+           "patch_tokens")
+
+
 def rmsnorm(delta: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor,
             out: torch.Tensor, eps: float, plus_one: bool) -> None:
     """residual += delta (if given); out = residual * rsqrt(mean(residual^2)+eps) * (weight [+1]).

@@ -45,6 +45,10 @@ class StepEntry:
     request: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()      # places among ``tokens`` whose logits are returned
+    # When set, the entry's single token is not ``tokens[0]`` (a placeholder) but
+    # element ``device_token`` of the ``token_source`` tensor given to the step:
+    # a token sampled on the device that the host has not read yet.
+    device_token: Optional[int] = None
 
 
 @dataclass
@@ -187,7 +191,8 @@ class Engine:
         self._turn_used = turn
         return self._pinned[turn]
 
-    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, torch.Tensor, int, bool]:
+    def prepare(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None
+                ) -> Tuple[StepContext, torch.Tensor, int, bool]:
         """Admit new requests, take pages for the step's tokens and stage the
         step's metadata on the device."""
         vocab = self.plan.vocab_size
@@ -208,6 +213,10 @@ class Engine:
                     raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
             if arr.min() < 0 or arr.max() >= vocab:
                 raise ValueError(f"request {e.request!r}: a token id is outside the vocabulary 0..{vocab - 1}")
+            if e.device_token is not None:
+                if n != 1 or token_source is None or not 0 <= e.device_token < token_source.numel():
+                    raise ValueError(f"request {e.request!r}: a token on the device stands for exactly one "
+                                     f"token and needs a token_source that holds it")
             token_arrays.append(arr.astype(np.int32))
         # New requests take a slot; every request takes the pages its tokens
         # need.  If that fails nothing of the step has run: requests that were
@@ -258,6 +267,12 @@ class Engine:
         for g in range(len(groups)):
             off[f"table{g}"] = cur
             cur = _align4(cur + S * width)
+        # after everything a captured graph reads, so that those offsets do not move
+        patches = [(s.q_start, e.device_token) for e, s in zip(entries, segments)
+                   if e.device_token is not None]
+        for name in ("patch_rows", "patch_src"):
+            off[name] = cur
+            cur = _align4(cur + len(patches))
         host = self._staging(cur)
         h = host.numpy()
         rows: List[int] = []
@@ -286,6 +301,10 @@ class Engine:
             tiles = np.asarray(pf_tiles, dtype=np.int32)
             h[off["pf_tile_seg"]: off["pf_tile_seg"] + len(pf_tiles)] = tiles[:, 0]
             h[off["pf_tile_q0"]: off["pf_tile_q0"] + len(pf_tiles)] = tiles[:, 1]
+        if patches:
+            pp = np.asarray(patches, dtype=np.int32)
+            h[off["patch_rows"]: off["patch_rows"] + len(patches)] = pp[:, 0]
+            h[off["patch_src"]: off["patch_src"] + len(patches)] = pp[:, 1]
         dev = self._meta_dev
         self._last_meta_ints = cur
         dev[:cur].copy_(host[:cur], non_blocking=True)
@@ -293,6 +312,10 @@ class Engine:
 
         def sec(name: str, size: int) -> torch.Tensor:
             return dev[off[name]: off[name] + size]
+
+        if patches:
+            ops.patch_tokens(sec("token_ids", T), sec("patch_rows", len(patches)), token_source,
+                             sec("patch_src", len(patches)), vocab)
 
         ctx = StepContext(
             device=self.device, dtype=self.dtype, segments=segments, num_tokens=T,
@@ -313,13 +336,16 @@ class Engine:
         in_order = N == T and rows == list(range(T))
         return ctx, sec("logit_rows", N), N, in_order
 
-    def step(self, entries: Sequence[StepEntry], probe: Optional[Dict[str, Any]] = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], probe: Optional[Dict[str, Any]] = None,
+             token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` on the
-        device, in the order of the entries and of their ``want`` lists."""
+        device, in the order of the entries and of their ``want`` lists.
+        ``token_source`` (int32, on the device) holds the tokens of entries
+        that name a ``device_token``."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if not entries:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
-        ctx, logit_rows, N, in_order = self.prepare(entries)
+        ctx, logit_rows, N, in_order = self.prepare(entries, token_source)
         ctx.probe = probe
         self.last_meta_ints = self._last_meta_ints
         self.storage.clear_state(self.cache.take_fresh_slots())

@@ -48,6 +48,7 @@ class Request:
     max_tokens: int = 0               # after clamping to the room left
     finish_reason: Optional[str] = None
     reserved: List[int] = field(default_factory=list)   # worst-case pages per group
+    inflight: int = 0                 # sampling entries planned whose token is not yet recorded
 
     @property
     def finished(self) -> bool:
@@ -59,6 +60,8 @@ class PlannedEntry:
     request: Request
     tokens: List[int]
     samples: bool          # True: the step's last token of this entry yields a new token
+    from_device: bool = False   # the (single) input token is the one the previous step sampled,
+                                # not yet read back: ``tokens`` holds a placeholder
 
 
 class Scheduler:
@@ -123,8 +126,18 @@ class Scheduler:
         portions in arrival order while budget, slots and pages last."""
         entries: List[PlannedEntry] = []
         for r in self.running:
-            last = r.output[-1]
-            entries.append(PlannedEntry(r, [last], True))
+            # A step may be planned while the one before it is still running
+            # (its tokens not yet recorded): the request's input is then the token
+            # on the device, and a request whose last token is among those in
+            # flight gets no further step.  Whether it stopped on an EOS is only
+            # known later; such a step's token is dropped by complete().
+            if len(r.output) + r.inflight >= r.max_tokens:
+                continue
+            if r.inflight:
+                entries.append(PlannedEntry(r, [0], True, True))
+            else:
+                entries.append(PlannedEntry(r, [r.output[-1]], True))
+            r.inflight += 1
         budget = self.max_step_tokens - len(entries)
         while budget > 0:
             r = self.prefilling
@@ -136,10 +149,13 @@ class Scheduler:
             take = min(budget, len(r.prompt) - r.prompt_done)
             whole = r.prompt_done + take == len(r.prompt)
             entries.append(PlannedEntry(r, r.prompt[r.prompt_done:r.prompt_done + take], whole))
+            r.prompt_done += take           # progress is booked when planned
             budget -= take
             if not whole:
                 break
             self.prefilling = None
+            r.inflight += 1
+            self.running.append(r)
         return entries
 
     # ---- after the step ----------------------------------------------------------
@@ -150,15 +166,13 @@ class Scheduler:
         it = iter(sampled)
         for e in entries:
             r = e.request
-            was_prompt = r.prompt_done < len(r.prompt)
-            if was_prompt:
-                r.prompt_done += len(e.tokens)
             if not e.samples:
                 continue
             token = int(next(it))
+            r.inflight -= 1
+            if r.finished:
+                continue        # planned ahead before its EOS was read: the token is dropped
             r.output.append(token)
-            if was_prompt:
-                self.running.append(r)
             if token in self.eos or token in r.params.stop_token_ids:
                 if not r.params.ignore_eos:
                     r.finish_reason = "stop"

@@ -45,6 +45,18 @@ def _eos_ids(folder: Optional[str], config: Dict[str, Any]) -> List[int]:
     return sorted(set(ids))
 
 
+class _InFlight:
+    """A launched step whose sampled tokens have not been read yet."""
+
+    def __init__(self, plan: List[PlannedEntry], count: int, index_of: Dict[Any, int]):
+        self.plan = plan
+        self.count = count                  # entries that sample
+        self.index_of = index_of            # request id -> place among the sampled tokens
+        self.tokens_dev: Optional[torch.Tensor] = None
+        self.tokens_host: Optional[torch.Tensor] = None
+        self.event: Optional[torch.cuda.Event] = None
+
+
 class LLM:
     def __init__(self, model_path: str, dtype: Union[torch.dtype, str] = torch.bfloat16, *,
                  max_running_req: int = 4, page_size: int = 64,
@@ -78,6 +90,10 @@ class LLM:
         self.sampler = Sampler(self.engine.device, self.engine.vocab_size)
         self.tokenizer = None
         self._counter = 0
+        self._inflight: Optional[_InFlight] = None
+        self._flip = 0
+        self._tok_dev: List[Optional[torch.Tensor]] = [None, None]
+        self._tok_host: List[Optional[torch.Tensor]] = [None, None]
         self.steps_since_check = 0
 
     # ---- text ------------------------------------------------------------
@@ -110,8 +126,12 @@ class LLM:
             rngs[uid] = RequestRng(sp.seed if sp.seed is not None else self.seed * 1000003 + uid)
             requests.append(r)
             self.scheduler.submit(r)
-        while self.scheduler.has_work():
-            self.run_step(rngs)
+        overlap = os.environ.get("FREETOKEN_DISABLE_OVERLAP_SCHEDULING", "0") in ("", "0")
+        while self.scheduler.has_work() or self._inflight is not None:
+            if overlap:
+                self.run_step_overlapped(rngs)
+            else:
+                self.run_step(rngs)
         self.engine.check_status()
         self.scheduler.finished.clear()
         results = []
@@ -124,21 +144,78 @@ class LLM:
         return results
 
     def run_step(self, rngs: Dict[Any, RequestRng]) -> List[Request]:
-        """Plan one step, run it, sample, record; returns finished requests."""
+        """Plan one step, run it, sample, read the tokens, record; returns
+        finished requests."""
+        done = self.drain()
+        step = self._launch(rngs)
+        if step is None:
+            if not done:
+                raise RuntimeError("the scheduler has work but could plan nothing: the page pool is too small")
+            return done
+        self._inflight = step
+        return done + self.drain()
+
+    def run_step_overlapped(self, rngs: Dict[Any, RequestRng]) -> List[Request]:
+        """Launch the next step BEFORE reading the tokens of the one in flight:
+        the host's planning, staging and bookkeeping of step N+1 run while the
+        device works on step N, and the tokens step N sampled reach step N+1 on
+        the device.  Returns the requests that finished in the step that was
+        read (one step late).  A request that turns out to have stopped on an
+        EOS has one token too many computed; the scheduler drops it.
+
+        The reference overlaps the same way (python/freetoken/scheduler/scheduler.py:
+        197-251, results drained one iteration late) and switches it off with the
+        same variable, ``FREETOKEN_DISABLE_OVERLAP_SCHEDULING``."""
+        step = self._launch(rngs)
+        done = self.drain()
+        if step is None and not done and self.scheduler.has_work():
+            step = self._launch(rngs)       # everything waited for the drain (nothing was in flight)
+            if step is None:
+                raise RuntimeError("the scheduler has work but could plan nothing: the page pool is too small")
+        self._inflight = step
+        return done
+
+    def _launch(self, rngs: Dict[Any, RequestRng]) -> Optional["_InFlight"]:
+        """Plan a step and put it on the device: metadata copy, step, sampling
+        and the copy of the sampled tokens to pinned memory, none waited for."""
         plan = self.scheduler.plan()
         if not plan:
-            raise RuntimeError("the scheduler has work but could plan nothing: the page pool is too small")
-        entries = [StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.samples else [])
-                   for e in plan]
-        logits = self.engine.step(entries)
+            return None
+        prev = self._inflight
+        entries = []
+        for e in plan:
+            src = prev.index_of[e.request.id] if e.from_device else None
+            entries.append(StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.samples else [], src))
+        logits = self.engine.step(entries, token_source=prev.tokens_dev if prev is not None else None)
         samplers = [e.request for e in plan if e.samples]
-        sampled: List[int] = []
+        step = _InFlight(plan, len(samplers), {r.id: i for i, r in enumerate(samplers)})
         if samplers:
+            k = self._flip
+            self._flip ^= 1
+            rows = max(len(samplers), 64)
+            if self._tok_dev[k] is None or self._tok_dev[k].numel() < rows:
+                self._tok_dev[k] = torch.empty(rows, dtype=torch.int32, device=self.engine.device)
+                self._tok_host[k] = torch.empty(rows, dtype=torch.int32).pin_memory()
             params = [r.params for r in samplers]
             uniforms = [0.0 if r.params.is_greedy else rngs[r.id].next_uniform() for r in samplers]
-            sampled = self.sampler.sample(logits, params, uniforms).cpu().tolist()
+            step.tokens_dev = self.sampler.sample(logits, params, uniforms, out=self._tok_dev[k])
+            step.tokens_host = self._tok_host[k]
+            step.tokens_host[:len(samplers)].copy_(step.tokens_dev, non_blocking=True)
+            step.event = torch.cuda.Event()
+            step.event.record()
+        return step
+
+    def drain(self) -> List[Request]:
+        """Wait for the step in flight (if any), read its tokens, record them."""
+        step, self._inflight = self._inflight, None
+        if step is None:
+            return []
+        sampled: List[int] = []
+        if step.count:
+            step.event.synchronize()
+            sampled = step.tokens_host[:step.count].tolist()
             self.steps_since_check += 1
             if self.steps_since_check >= 64:
                 self.steps_since_check = 0
                 self.engine.check_status()
-        return self.scheduler.complete(plan, sampled)
+        return self.scheduler.complete(step.plan, sampled)

@@ -41,12 +41,16 @@ class Sampler:
         self._out: Optional[torch.Tensor] = None
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-               uniforms: Sequence[float]) -> torch.Tensor:
-        """``logits`` ``[rows, vocab]`` float32 on the device -> int32 ``[rows]`` there."""
+               uniforms: Sequence[float], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``logits`` ``[rows, vocab]`` float32 on the device -> int32 ``[rows]`` there
+        (in ``out`` if given, else in a buffer the next call overwrites)."""
         rows = logits.shape[0]
-        if self._out is None or self._out.numel() < rows:
-            self._out = torch.empty(max(rows, 64), dtype=torch.int32, device=self.device)
-        out = self._out[:rows]
+        if out is not None:
+            out = out[:rows]
+        else:
+            if self._out is None or self._out.numel() < rows:
+                self._out = torch.empty(max(rows, 64), dtype=torch.int32, device=self.device)
+            out = self._out[:rows]
         if all(p.is_greedy for p in params):
             ops.sample(logits, None, None, None, None, out, None)
             return out

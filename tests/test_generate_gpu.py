@@ -107,3 +107,46 @@ def test_eos_stops_generation(folder_a):
         pytest.skip("the chosen stop token appears earlier")
     out = llm.generate([prompt], SamplingParams(max_tokens=8, stop_token_ids=[stop_at]))[0]
     assert out["token_ids"] == free[:3] and out["finish_reason"] == "stop"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_scheduling_gives_the_same_tokens(folder_c, dtype, monkeypatch):
+    """Steps launched before the previous step's tokens are read (inputs handed on
+    on the device, results read one step late) against the synchronous loop:
+    greedy and seeded sampling, stops on a token in mid-flight, more requests
+    than slots so that pages and slots are reused."""
+    from freetoken_b200 import LLM, SamplingParams
+    vocab = tiny.TINY_C["vocab_size"]
+    prompts = [tiny.tokens(20 + i, n, vocab) for i, n in enumerate((3, 18, 40, 9, 27, 5))]
+    llm = LLM(folder_c, dtype, page_size=16, num_token_override=256, max_running_req=3,
+              max_extend_tokens=24)
+
+    def both(params):
+        monkeypatch.setenv("FREETOKEN_DISABLE_OVERLAP_SCHEDULING", "1")
+        sync = llm.generate(prompts, params)
+        monkeypatch.setenv("FREETOKEN_DISABLE_OVERLAP_SCHEDULING", "0")
+        replays = llm.engine.graph_replays
+        over = llm.generate(prompts, params)
+        llm.scheduler.check_integrity()
+        assert llm.engine.cache.free_pages() == llm.engine.cache.total_pages()
+        return sync, over, llm.engine.graph_replays - replays
+
+    greedy = [SamplingParams(max_tokens=12 + 3 * i, ignore_eos=True) for i in range(len(prompts))]
+    sync, over, replays = both(greedy)
+    assert [r["token_ids"] for r in sync] == [r["token_ids"] for r in over]
+    if dtype == "bfloat16":
+        assert replays > 0, "decode-only steps of the overlapped loop did not replay a graph"
+    # stop on a token that the free run produced in the middle of two requests
+    stops = []
+    for r in sync:
+        t = r["token_ids"]
+        stops.append([t[5]] if len(t) > 5 else [])
+    stopping = [SamplingParams(max_tokens=p.max_tokens, stop_token_ids=s) for p, s in zip(greedy, stops)]
+    sync2, over2, _ = both(stopping)
+    assert [(r["token_ids"], r["finish_reason"]) for r in sync2] == \
+        [(r["token_ids"], r["finish_reason"]) for r in over2]
+    assert any(r["finish_reason"] == "stop" for r in sync2)
+    sampled = [SamplingParams(temperature=0.9, top_p=0.95, max_tokens=10, ignore_eos=True, seed=7 + i)
+               for i in range(len(prompts))]
+    sync3, over3, _ = both(sampled)
+    assert [r["token_ids"] for r in sync3] == [r["token_ids"] for r in over3]

@@ -149,3 +149,51 @@ def test_random_workloads_finish_with_nothing_left_behind(seed):
         assert steps < 2000
     assert all(r.finish_reason == "length" and len(r.output) == r.max_tokens for r in accepted)
     assert cache.free_pages() == cache.total_pages() and cache.free_slots == cache.max_slots
+
+
+def _grow(cache, plan):
+    for e in plan:
+        cache.grow(e.request.id, cache.length(e.request.id) + len(e.tokens))
+        cache.advance(e.request.id, len(e.tokens))
+
+
+def test_a_step_planned_before_the_last_one_is_recorded_takes_its_token_from_the_device():
+    sched, cache = make(budget=8)
+    sched.submit(req("a", 3, max_tokens=3))
+    p1 = sched.plan()                                 # whole prompt, first token in flight
+    _grow(cache, p1)
+    assert [(e.samples, e.from_device) for e in p1] == [(True, False)]
+    p2 = sched.plan()                                 # planned ahead: input is the token on the device
+    _grow(cache, p2)
+    assert [(len(e.tokens), e.samples, e.from_device) for e in p2] == [(1, True, True)]
+    assert sched.complete(p1, [11]) == []
+    p3 = sched.plan()                                 # token 2 still in flight
+    _grow(cache, p3)
+    assert [e.from_device for e in p3] == [True]
+    assert sched.plan() == []                         # three tokens planned: max_tokens reached
+    assert sched.complete(p2, [12]) == []
+    done = sched.complete(p3, [13])
+    assert [r.id for r in done] == ["a"] and done[0].output == [11, 12, 13]
+    assert done[0].finish_reason == "length" and done[0].inflight == 0
+    sched.check_integrity()
+    assert cache.free_pages() == cache.total_pages()
+
+
+def test_a_token_computed_past_an_eos_is_dropped():
+    sched, cache = make(budget=8, eos=[99])
+    sched.submit(req("a", 2, max_tokens=6))
+    sched.submit(req("b", 2, max_tokens=6))
+    p1 = sched.plan()
+    _grow(cache, p1)
+    p2 = sched.plan()                                 # both planned ahead
+    _grow(cache, p2)
+    done = sched.complete(p1, [99, 5])                # a stopped; its entry in p2 is already running
+    assert [r.id for r in done] == ["a"] and done[0].finish_reason == "stop"
+    assert not cache.has_request("a")                 # what it held is given back at once
+    p3 = sched.plan()
+    _grow(cache, p3)
+    assert [e.request.id for e in p3] == ["b"]
+    assert sched.complete(p2, [42, 6]) == []          # a's extra token is dropped
+    assert done[0].output == [99]
+    assert sched.running[0].output == [5, 6]
+    sched.check_integrity()
