@@ -64,9 +64,11 @@ __device__ __forceinline__ float glu_act_s(float g, float u, int act, float alph
   return (g / (1.f + __expf(-alpha * g))) * (u + 1.f);
 }
 
-constexpr int KS = 4;  // warps per block, splitting K
-
-template <int NT, bool GLU, typename OT>
+// KS: warps per block, splitting K.  4 for the expert banks and the head (many
+// blocks); 8 or 16 for dense matrices with few rows (QKV, O), where 4 warps per
+// 16 weight rows would leave an SM with a handful of warps and too few loads in
+// flight to fill the memory pipe.  KS is chosen from the weight's shape alone.
+template <int NT, bool GLU, typename OT, int KS>
 __global__ void __launch_bounds__(KS * 32) skinny_kernel(SkinnyArgs a) {
   constexpr int U = NT == 1 ? 4 : (NT == 2 ? 2 : 1);  // 32-k chunks in flight per warp
   constexpr int NG = GLU ? 2 : 1;
@@ -184,15 +186,27 @@ __global__ void __launch_bounds__(KS * 32) skinny_kernel(SkinnyArgs a) {
   }
 }
 
-template <bool GLU, typename OT>
+template <bool GLU, typename OT, int KS>
 int launch_nt(const SkinnyArgs& a, int nt, dim3 grid, cudaStream_t stream) {
   switch (nt) {
-    case 1: launch_pdl(skinny_kernel<1, GLU, OT>, grid, dim3(KS * 32), 0, stream, a); break;
-    case 2: launch_pdl(skinny_kernel<2, GLU, OT>, grid, dim3(KS * 32), 0, stream, a); break;
-    case 4: launch_pdl(skinny_kernel<4, GLU, OT>, grid, dim3(KS * 32), 0, stream, a); break;
+    case 1: launch_pdl(skinny_kernel<1, GLU, OT, KS>, grid, dim3(KS * 32), 0, stream, a); break;
+    case 2: launch_pdl(skinny_kernel<2, GLU, OT, KS>, grid, dim3(KS * 32), 0, stream, a); break;
+    case 4: launch_pdl(skinny_kernel<4, GLU, OT, KS>, grid, dim3(KS * 32), 0, stream, a); break;
     default: return FT_ERR_SHAPE;
   }
   return FT_OK;
+}
+
+// Warps per block for a dense [N, K] weight: doubled from 4 while the launch
+// would hold fewer than about 20 warps per SM and a warp keeps at least 8
+// chunks of 32 k.  A function of the weight's shape only, so a token's result
+// does not depend on what else is in the batch.
+static int dense_k_split(int N, int K) {
+  const long long tiles = (N + 15) / 16;
+  const int chunks = (K + 31) / 32;
+  int ks = 4;
+  while (ks < 16 && tiles * ks < 3000 && chunks / (2 * ks) >= 8) ks *= 2;
+  return ks;
 }
 
 }  // namespace ft
@@ -218,12 +232,17 @@ extern "C" int ft_skinny_gemm(const void* A, long long lda, const void* W,
   dim3 grid((N + 15) / 16, active ? min(G, M) : G);
   const int nt = rows_per_pass / 8;
   int rc;
+  const int ks = (!glu && !group_offsets && G == 1) ? dense_k_split(N, K) : 4;
   if (c_dtype == FT_DTYPE_BF16) {
-    rc = glu ? launch_nt<true, __nv_bfloat16>(a, nt, grid, stream)
-             : launch_nt<false, __nv_bfloat16>(a, nt, grid, stream);
+    if (glu) rc = launch_nt<true, __nv_bfloat16, 4>(a, nt, grid, stream);
+    else if (ks == 16) rc = launch_nt<false, __nv_bfloat16, 16>(a, nt, grid, stream);
+    else if (ks == 8) rc = launch_nt<false, __nv_bfloat16, 8>(a, nt, grid, stream);
+    else rc = launch_nt<false, __nv_bfloat16, 4>(a, nt, grid, stream);
   } else if (c_dtype == FT_DTYPE_F32) {
-    rc = glu ? launch_nt<true, float>(a, nt, grid, stream)
-             : launch_nt<false, float>(a, nt, grid, stream);
+    if (glu) rc = launch_nt<true, float, 4>(a, nt, grid, stream);
+    else if (ks == 16) rc = launch_nt<false, float, 16>(a, nt, grid, stream);
+    else if (ks == 8) rc = launch_nt<false, float, 8>(a, nt, grid, stream);
+    else rc = launch_nt<false, float, 4>(a, nt, grid, stream);
   } else {
     return FT_ERR_DTYPE;
   }

@@ -31,6 +31,7 @@ def main(argv=None) -> int:
     a = p.parse_args(argv)
     cfg = dict(BENCH_CONFIG)
     cfg["num_hidden_layers"] = a.layers
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], a.context + 256)
     engine = Engine.from_config(cfg, 0, EngineArgs(
         dtype="bfloat16", page_size=64, max_tokens=a.batch * (a.context + 128) + a.context + 64,
         max_running_requests=a.batch + 1))
