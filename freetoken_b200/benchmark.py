@@ -231,8 +231,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     with ClockSampler() as prefill_clocks:
         prefill_ms = timed(prefill_once, 5)
     pf = prefill_flops(cfg, layers, a.prefill_tokens)
+    # what bounds this step: a 2,048-token portion sends about 64 rows to each of the
+    # experts, so every expert's weights are read for a few rows each; hbm_frac is the
+    # weight bytes of the step (all experts counted as touched) over its time
+    pf_bytes = step_bytes(cfg, layers, 1, a.prefill_tokens, [cfg["num_local_experts"]] * layers)
     prefill = {"value": a.prefill_tokens / (prefill_ms / 1e3), "tokens": a.prefill_tokens,
-               "ms": prefill_ms, "frac": pf / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12)}
+               "ms": prefill_ms, "frac": pf / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12),
+               "hbm_frac": pf_bytes / (prefill_ms / 1e3) / (peaks["hbm_gbs"] * 1e9)}
 
     # ---- decode at each batch size -----------------------------------------
     def fill_contexts(batch: int) -> List[str]:
