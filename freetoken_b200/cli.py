@@ -70,6 +70,10 @@ def _run_generate(argv: Sequence[str]) -> int:
     p.add_argument("--top-k", type=int, default=-1)
     p.add_argument("--top-p", type=float, default=1.0)
     p.add_argument("--ignore-eos", action="store_true")
+    p.add_argument("--stop", action="append", default=[],
+                   help="stop string (needs a tokenizer); repeat for several")
+    p.add_argument("--stop-token-id", action="append", type=int, default=[],
+                   help="token id that ends a request; repeat for several")
     a = p.parse_args(argv)
     from .llm import LLM
     from .sampling import SamplingParams
@@ -84,7 +88,8 @@ def _run_generate(argv: Sequence[str]) -> int:
               memory_ratio=a.memory_ratio, use_dummy_weight=a.use_dummy_weight,
               cuda_graph_max_bs=a.cuda_graph_max_bs, seed=a.seed)
     sp = SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
-                        ignore_eos=a.ignore_eos, max_tokens=a.max_tokens, seed=a.seed)
+                        ignore_eos=a.ignore_eos, max_tokens=a.max_tokens, seed=a.seed,
+                        stop_strs=[x for x in a.stop if x], stop_token_ids=a.stop_token_id)
     for prompt, result in zip(prompts, llm.generate(prompts, sp)):
         print(json.dumps({"prompt": prompt, **result}))
     return 0

@@ -66,12 +66,13 @@ class PlannedEntry:
 
 class Scheduler:
     def __init__(self, cache: CacheManager, max_step_tokens: int = 8192,
-                 eos_token_ids: Iterable[int] = ()):
+                 eos_token_ids: Iterable[int] = (), detokenize=None):
         if max_step_tokens < 1:
             raise ValueError("max_step_tokens must be at least 1")
         self.cache = cache
         self.max_step_tokens = max_step_tokens
         self.eos = set(int(t) for t in eos_token_ids)
+        self.detokenize = detokenize          # token ids -> text, for stop strings
         self.pending: Deque[Request] = deque()
         self.prefilling: Optional[Request] = None      # admitted, prompt not yet whole
         self.running: List[Request] = []               # decoding
@@ -176,6 +177,8 @@ class Scheduler:
             if token in self.eos or token in r.params.stop_token_ids:
                 if not r.params.ignore_eos:
                     r.finish_reason = "stop"
+            if r.finish_reason is None and r.params.stop_strs and self._stop_str_shows(r):
+                r.finish_reason = "stop"
             if r.finish_reason is None and len(r.output) >= r.max_tokens:
                 r.finish_reason = "length"
             if r.finish_reason is not None:
@@ -183,6 +186,17 @@ class Scheduler:
         for r in done:
             self._retire(r)
         return done
+
+    def _stop_str_shows(self, r: Request) -> bool:
+        """Whether a stop string shows in the text of the newest tokens: a stop of
+        N characters spans at most N tokens, so only that tail is decoded
+        (python/freetoken/scheduler/scheduler.py:420-434)."""
+        stops = [s for s in r.params.stop_strs if s]
+        if not stops or self.detokenize is None:
+            return False
+        tail = r.output[-(max(len(s) for s in stops) + 1):]
+        text = self.detokenize(tail)
+        return any(s in text for s in stops)
 
     def _retire(self, r: Request) -> None:
         if r in self.running:

@@ -118,6 +118,9 @@ class LLM:
             raise ValueError("one SamplingParams per prompt, or one for all")
         requests: List[Request] = []
         rngs: Dict[Any, RequestRng] = {}
+        if any(sp.stop_strs for sp in sampling_params):
+            tok = self._tokenizer()             # raises if the folder has none
+            self.scheduler.detokenize = tok.decode
         for prompt, sp in zip(prompts, sampling_params):
             ids = self._tokenizer().encode(prompt) if isinstance(prompt, str) else list(prompt)
             uid = self._counter

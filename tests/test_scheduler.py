@@ -197,3 +197,15 @@ def test_a_token_computed_past_an_eos_is_dropped():
     assert done[0].output == [99]
     assert sched.running[0].output == [5, 6]
     sched.check_integrity()
+
+
+def test_a_stop_string_in_the_newest_text_stops_the_request():
+    words = {1: "a", 2: "b", 3: " EN", 4: "D ", 5: "c"}
+    cache = CacheManager([PagedKVNeed(2, 16, None)], 4, 16, 4, 64)
+    sched = Scheduler(cache, 8, (), detokenize=lambda ids: "".join(words[i] for i in ids))
+    sched.submit(Request("a", [1, 2], SamplingParams(max_tokens=10, stop_strs=["END", ""])))
+    out = iter([1, 3, 4, 5, 5])
+    while sched.has_work():
+        run_step(sched, cache, token_of=lambda r: next(out))
+    r = sched.finished[0]
+    assert r.output == [1, 3, 4] and r.finish_reason == "stop"     # "a EN" + "D " holds "END"
