@@ -38,6 +38,21 @@ BENCH_CONFIG: Dict[str, Any] = dict(
     routed_scaling_factor=1.0, hidden_act="silu", vocab_size=200064, tie_word_embeddings=False,
 )
 FAMILY_LAYERS = 62
+
+
+def bench_random_options():
+    """Scales of the benchmark's random weights.  With every matrix ~N(0, 0.02^2) the
+    hidden states of a prompt's tokens are dominated by what the layers add (the
+    attention of a random model averages over the prefix), the router sees almost the
+    same vector at every position and from the second layer on about 60 of the 256
+    experts get all tokens of a 2,048-token prompt - a prefill that reads a quarter of
+    the weights a trained model's balanced routing reads.  Embedding rows of unit
+    variance and residual-writing matrices scaled by 1/sqrt(2 * layers of the family),
+    both usual initialisations, keep the token's own signal on top: every layer then
+    routes like the first one (256 of 256 experts touched, the busiest with under twice
+    the mean load)."""
+    from .weights import RandomOptions
+    return RandomOptions(embedding_std=1.0, residual_out_scale=(2.0 * FAMILY_LAYERS) ** -0.5)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -199,6 +214,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     peaks = load_peaks()
     t0 = time.time()
     llm = LLM("", a.dtype, config=cfg, use_dummy_weight=True, seed=a.seed,
+              dummy_weight_options=bench_random_options(),
               max_running_req=max_batch + 1, page_size=page, num_token_override=pool_tokens,
               max_extend_tokens=8192, max_seq_len_override=room + page)
     engine = llm.engine
@@ -231,13 +247,19 @@ def main(argv: Optional[List[str]] = None) -> int:
     with ClockSampler() as prefill_clocks:
         prefill_ms = timed(prefill_once, 5)
     pf = prefill_flops(cfg, layers, a.prefill_tokens)
-    # what bounds this step: a 2,048-token portion sends about 64 rows to each of the
-    # experts, so every expert's weights are read for a few rows each; hbm_frac is the
-    # weight bytes of the step (all experts counted as touched) over its time
-    pf_bytes = step_bytes(cfg, layers, 1, a.prefill_tokens, [cfg["num_local_experts"]] * layers)
+    # what bounds this step: a 2,048-token portion sends a few dozen rows to each of
+    # the experts it touches, so their weights are read for a few rows each; hbm_frac is
+    # the weight bytes of the step (experts counted from the router in an untimed probe
+    # step, as for decode) over its time
+    pf_probe: Dict[str, Any] = {}
+    engine.step([StepEntry("prefill", rng.integers(0, V, a.prefill_tokens).tolist(), [])], probe=pf_probe)
+    engine.end_request("prefill")
+    pf_touched = pf_probe.get("experts_touched", [cfg["num_local_experts"]] * layers)
+    pf_bytes = step_bytes(cfg, layers, 1, a.prefill_tokens, pf_touched)
     prefill = {"value": a.prefill_tokens / (prefill_ms / 1e3), "tokens": a.prefill_tokens,
                "ms": prefill_ms, "frac": pf / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12),
-               "hbm_frac": pf_bytes / (prefill_ms / 1e3) / (peaks["hbm_gbs"] * 1e9)}
+               "hbm_frac": pf_bytes / (prefill_ms / 1e3) / (peaks["hbm_gbs"] * 1e9),
+               "experts_touched_per_layer": sum(pf_touched) / max(1, len(pf_touched))}
 
     # ---- decode at each batch size -----------------------------------------
     def fill_contexts(batch: int) -> List[str]:
@@ -313,7 +335,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         "value": main_r["tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": a.steps,
         "warmup": max(3, a.warmup), "ms_per_step": main_r["ms"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if a.dtype == "bfloat16" else "fp32",
-        "data": "synthetic: random weights, uniform random token ids", "impl": "ours",
+        "data": "synthetic: random weights (unit-variance embedding, residual outputs / sqrt(2*62): balanced routing), uniform random token ids", "impl": "ours",
         "config": {
             "model": "MiniMax-M3 real width", "layers": layers, "layers_in_family": FAMILY_LAYERS,
             "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],

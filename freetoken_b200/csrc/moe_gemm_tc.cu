@@ -38,9 +38,8 @@ namespace ft {
 
 constexpr int TC_BM = 128;         // weight rows per tile (UMMA M)
 constexpr int TC_BK = 64;          // k-block: 64 bf16 = 128 bytes = one swizzle row
-constexpr int TC_MAXN = 128;       // most tokens per tile (UMMA N)
+constexpr int TC_MAXN = 128;       // most tokens per tile (UMMA N); 256 in the wide build
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;     // 16 KB
-constexpr int TC_B_BYTES = TC_MAXN * TC_BK * 2;   // 16 KB reserved per stage
 
 struct TcArgs {
   void* C;
@@ -70,16 +69,22 @@ __device__ __forceinline__ float tc_glu(float g, float u, int act, float alpha, 
 // side by side share an expert.  The TMA ring never drains between tiles and the
 // accumulator is double-buffered in TMEM, so the epilogue of one tile runs under
 // the main loop of the next.
-template <bool GLU>
+// WIDE (down projection with many rows per expert): token tiles of up to 256,
+// so a weight tile is fetched half as often per product: at 128 x 128 both
+// operands are re-read for every tile and the shared-memory fill, not the
+// tensor core, sets the pace.
+template <bool GLU, bool WIDE>
 __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                           const __grid_constant__ CUtensorMap tm_x,
                                                           TcArgs a) {
+  static_assert(!(GLU && WIDE), "gate and up accumulators of a 256-token tile would fill all of TMEM");
   // a stage holds KSUB 64-wide k-blocks: one with GLU (two weight boxes per
   // k-block already), two without, so that every stage moves 40-48 KB and the
   // per-stage barrier round trip is paid half as often on the down projection
-  constexpr int KSUB = GLU ? 1 : 2;
+  constexpr int TC_B_BYTES = (WIDE ? 2 : 1) * TC_MAXN * TC_BK * 2;   // reserved per k-block
+  constexpr int KSUB = (GLU || WIDE) ? 1 : 2;
   constexpr int NA = GLU ? 2 : 1;                     // weight boxes per k-block
-  constexpr int STAGES = GLU ? 4 : 3;
+  constexpr int STAGES = (GLU || WIDE) ? 4 : 3;
   constexpr int STAGE_BYTES = KSUB * (NA * TC_A_BYTES + TC_B_BYTES);
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -154,14 +159,19 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // instruction descriptor: D f32, A/B bf16, both K-major, N, M = 128
-      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(ntok >> 3) << 17) |
-                             ((unsigned)(TC_BM >> 4) << 24);
       long long done = 0;             // k-blocks consumed so far
       int local = 0;                  // tiles this CTA has started
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        if (a.tile_expert[t / wtiles] < 0) continue;
+        const int y = t / wtiles;
+        const int e = a.tile_expert[y];
+        if (e < 0) continue;
+        // instruction descriptor: D f32, A/B bf16, both K-major, M = 128, N = the rows
+        // this tile really has, rounded up to 16: an expert's last tile costs what it holds
+        const int left = a.group_offsets[e + 1] - a.tile_row0[y];
+        const int n_tile = min(ntok, (left + 15) & ~15);
+        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n_tile >> 3) << 17) |
+                               ((unsigned)(TC_BM >> 4) << 24);
         const int b = local & 1;
         if (!mbar_wait(&acc_empty[b], ((unsigned)(local >> 1) & 1u) ^ 1u, &gave_up)) {
           atomicCAS(a.status, 0, 4);
@@ -210,32 +220,68 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
       const int row0 = a.tile_row0[y], row_end = a.group_offsets[e + 1];
       const int n = (t % wtiles) * TC_BM + lane_base + lane;
       const int b = local & 1;
+      const int n_tile = min(ntok, (row_end - row0 + 15) & ~15);
+      // Without GLU (the down projection) a column's output row and route weight come
+      // from two dependent loads from global memory: they are fetched for the whole
+      // tile before the wait on the accumulator, so that this tile's main loop hides
+      // them; lane l keeps columns l, l+32, ...; handed round by shuffle.  With GLU a
+      // column's output row is its sorted row and nothing is loaded.
+      constexpr int NQ = GLU ? 1 : (WIDE ? 2 : 1) * TC_MAXN / 32;
+      int my_crow[NQ];
+      float my_scale[NQ];
+      if (!GLU) {
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+          const int row = row0 + q * 32 + lane;
+          my_crow[q] = -1;
+          my_scale[q] = 1.f;
+          if (q * 32 + lane < n_tile && row < row_end) {
+            my_crow[q] = a.c_rows ? a.c_rows[row] : row;
+            if (a.row_scale) my_scale[q] = a.row_scale[my_crow[q]];
+          }
+        }
+      }
       bool ok = mbar_wait(&acc_full[b], (unsigned)(local >> 1) & 1u, &gave_up);
       if (!ok && lane == 0) { atomicCAS(a.status, 0, 3); gave_up = 1; }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
       const unsigned tmem_d = tmem_base + (unsigned)(b * acc_cols) + ((unsigned)lane_base << 16);
-      for (int c0 = 0; c0 < ntok; c0 += 16) {
-        // output row and route weight of column c0 + lane (lanes 0..15), handed round by shuffle
-        int my_crow = -1;
-        float my_scale = 1.f;
-        if (lane < 16 && row0 + c0 + lane < row_end) {
-          my_crow = a.c_rows ? a.c_rows[row0 + c0 + lane] : row0 + c0 + lane;
-          if (a.row_scale) my_scale = a.row_scale[my_crow];
-        }
-        unsigned g[16], u[16];
-        tc_ld16(tmem_d + (unsigned)c0, g);
-        if (GLU) tc_ld16(tmem_d + (unsigned)(c0 + ntok), u);
-        tc_ld_wait();
+      if (GLU) {
+        for (int c0 = 0; c0 < n_tile; c0 += 16) {
+          unsigned g[16], u[16];
+          tc_ld16(tmem_d + (unsigned)c0, g);
+          tc_ld16(tmem_d + (unsigned)(c0 + ntok), u);
+          tc_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const int crow = __shfl_sync(0xffffffffu, my_crow, c);
-          const float scale = __shfl_sync(0xffffffffu, my_scale, c);
-          if (crow >= 0 && n < a.n_out) {
-            float v = __uint_as_float(g[c]);
-            if (GLU) v = tc_glu(v, __uint_as_float(u[c]), a.act, a.act_alpha, a.act_limit);
-            C[(size_t)crow * a.ldc + n] = __float2bfloat16_rn(v * scale);
+          for (int c = 0; c < 16; ++c) {
+            const int row = row0 + c0 + c;
+            if (row < row_end && n < a.n_out) {
+              const int crow = a.c_rows ? a.c_rows[row] : row;
+              float v = tc_glu(__uint_as_float(g[c]), __uint_as_float(u[c]), a.act, a.act_alpha, a.act_limit);
+              if (a.row_scale) v *= a.row_scale[crow];
+              C[(size_t)crow * a.ldc + n] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int c0 = q * 32 + half * 16;
+            if (c0 < n_tile) {
+              unsigned g[16];
+              tc_ld16(tmem_d + (unsigned)c0, g);
+              tc_ld_wait();
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                const int crow = __shfl_sync(0xffffffffu, my_crow[q], half * 16 + c);
+                const float scale = __shfl_sync(0xffffffffu, my_scale[q], half * 16 + c);
+                if (crow >= 0 && n < a.n_out)
+                  C[(size_t)crow * a.ldc + n] = __float2bfloat16_rn(__uint_as_float(g[c]) * scale);
+              }
+            }
           }
         }
       }
@@ -369,7 +415,7 @@ int ft_moe_gemm_tc(const void* map_w, const void* map_x, void* C, long long ldc,
                    int ntok, int glu, int act, float act_alpha, float act_limit,
                    cudaStream_t stream) {
   if (rows_bound <= 0 || n_out <= 0) return FT_OK;
-  if (ntok < 16 || ntok > TC_MAXN || (ntok & 15) || (K & 7) || G <= 0) return FT_ERR_SHAPE;
+  if (ntok < 16 || ntok > (glu ? TC_MAXN : 2 * TC_MAXN) || (ntok & 15) || (K & 7) || G <= 0) return FT_ERR_SHAPE;
   CUtensorMap mw, mx;
   memcpy(&mw, map_w, sizeof(mw));
   memcpy(&mx, map_x, sizeof(mx));
@@ -384,24 +430,34 @@ int ft_moe_gemm_tc(const void* map_w, const void* map_x, void* C, long long ldc,
   }
   const int total = tiles_y * ((n_out + TC_BM - 1) / TC_BM);
   dim3 grid(total < sms ? total : sms);
+  constexpr int B_BYTES = TC_MAXN * TC_BK * 2;
   if (glu) {
-    const size_t smem = 4 * (2 * TC_A_BYTES + TC_B_BYTES) + 1024;
+    const size_t smem = 4 * (2 * TC_A_BYTES + B_BYTES) + 1024;
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    moe_gemm_tc_kernel<true><<<grid, 192, smem, stream>>>(mw, mx, a);
+    moe_gemm_tc_kernel<true, false><<<grid, 192, smem, stream>>>(mw, mx, a);
+  } else if (ntok > TC_MAXN) {
+    const size_t smem = 4 * (TC_A_BYTES + 2 * B_BYTES) + 1024;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    moe_gemm_tc_kernel<false, true><<<grid, 192, smem, stream>>>(mw, mx, a);
   } else {
-    const size_t smem = 3 * 2 * (TC_A_BYTES + TC_B_BYTES) + 1024;
+    const size_t smem = 3 * 2 * (TC_A_BYTES + B_BYTES) + 1024;
     static bool configured = false;
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
       configured = true;
     }
-    moe_gemm_tc_kernel<false><<<grid, 192, smem, stream>>>(mw, mx, a);
+    moe_gemm_tc_kernel<false, false><<<grid, 192, smem, stream>>>(mw, mx, a);
   }
   FT_LAUNCH_CHECK();
   return FT_OK;

@@ -343,19 +343,26 @@ def moe_gemm_tc_takes(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool
             and c.stride(1) == 1)
 
 
-def tc_tokens_per_tile(rows: int, groups: int) -> int:
-    """Tokens per MMA tile for ``rows`` sorted rows over ``groups`` experts."""
+def tc_tokens_per_tile(rows: int, groups: int, wide: bool = False) -> int:
+    """Most tokens of an MMA tile for ``rows`` sorted rows over ``groups`` experts.
+    A tile's product is as wide as the rows it really holds (rounded up to 16), so
+    a large tile costs nothing extra and saves fetching an expert's weights once
+    more for a few rows beyond a small tile: 128, or - for a product without GLU
+    (``wide``) when that lets most experts fit one tile - 256."""
     avg = -(-rows // max(1, groups))
-    return min(128, max(16, -(-avg // 16) * 16))
+    if wide and 104 <= avg <= 208:
+        return 256
+    return 128
 
 
 def moe_tile_map(group_offsets: torch.Tensor, active: torch.Tensor, rows: int, groups: int,
-                 tokens_per_tile: int, workspace) -> tuple:
+                 tokens_per_tile: int, workspace, tag: str = "") -> tuple:
     """``(tile_expert, tile_row0)`` for the tcgen05 grouped GEMM: one entry per
-    (busy expert, tile of ``tokens_per_tile`` sorted rows)."""
+    (busy expert, tile of ``tokens_per_tile`` sorted rows).  ``tag`` names the
+    buffers when a step keeps two maps (two tile sizes)."""
     bound = -(-rows // tokens_per_tile) + min(groups, rows)
-    tile_expert = workspace.get("moe.tile_expert", (bound,), torch.int32)
-    tile_row0 = workspace.get("moe.tile_row0", (bound,), torch.int32)
+    tile_expert = workspace.get("moe.tile_expert" + tag, (bound,), torch.int32)
+    tile_row0 = workspace.get("moe.tile_row0" + tag, (bound,), torch.int32)
     f = _fn("moe_gemm_tc", "ft_moe_tile_map", "p p p p i i i")
     _check(f(_ptr(group_offsets), _ptr(active), _ptr(tile_expert), _ptr(tile_row0), rows, groups,
              tokens_per_tile, _stream()), "moe_tile_map")

@@ -64,10 +64,12 @@ class LLM:
                  max_extend_tokens: int = 8192, max_seq_len_override: Optional[int] = None,
                  memory_ratio: float = 0.9, use_dummy_weight: bool = False,
                  cuda_graph_max_bs: int = 64, seed: int = 0,
-                 device: str = "cuda:0", config: Optional[Dict[str, Any]] = None):
+                 device: str = "cuda:0", config: Optional[Dict[str, Any]] = None,
+                 dummy_weight_options=None):
         """``model_path``: a folder with ``config.json`` and safetensors files.
         With ``use_dummy_weight`` only ``config.json`` (or ``config``) is
-        needed and weights are random from ``seed``."""
+        needed and weights are random from ``seed`` (scales from
+        ``dummy_weight_options``, a :class:`freetoken_b200.weights.RandomOptions`)."""
         args = EngineArgs(dtype=dtype, device=device, page_size=page_size,
                           num_pages=num_page_override, max_tokens=num_token_override,
                           max_running_requests=max_running_req, max_seq_len=max_seq_len_override,
@@ -80,7 +82,10 @@ class LLM:
             with open(os.path.join(model_path, "config.json")) as f:
                 raw = json.load(f)
         if use_dummy_weight:
-            self.engine = Engine.from_config(raw, seed, args)
+            if dummy_weight_options is not None:
+                self.engine = Engine.from_config(raw, seed, args, random_options=dummy_weight_options)
+            else:
+                self.engine = Engine.from_config(raw, seed, args)
         else:
             self.engine = Engine.from_folder(model_path, args)
         self.model_path = model_path

@@ -76,7 +76,7 @@ class PagedAttention(Mixer):
                 Name(self._split[0], (qn, self.hidden)),
                 Name(self._split[1], (kn, self.hidden)),
                 Name(self._split[2], (kn, self.hidden))), 0),)),
-            TensorSpec(self.n_o, (self.hidden, qn)),
+            TensorSpec(self.n_o, (self.hidden, qn), tag="residual_out"),
         ]
         if self.norm_mode:
             sizes = (qn, kn) if self.norm_mode == 1 else (self.d, self.d)

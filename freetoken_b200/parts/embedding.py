@@ -30,7 +30,7 @@ class TokenEmbedding(Embedding):
         self.weight = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.weight_name, (self.vocab, self.hidden))]
+        return [TensorSpec(self.weight_name, (self.vocab, self.hidden), tag="embedding")]
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype) -> None:
         self.weight = tensors[self.weight_name]

@@ -98,7 +98,7 @@ class RoutedExperts(FeedForward):
                        init=Init(0.0, 0.01 if self.use_bias else 0.0), tag="router_bias",
                        optional=not self.use_bias),
             TensorSpec(self.n_gate_up, (E, 2 * I, H), sources=(gate_up,)),
-            TensorSpec(self.n_down, (E, H, I), sources=(down,)),
+            TensorSpec(self.n_down, (E, H, I), sources=(down,), tag="residual_out"),
         ]
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype) -> None:
@@ -176,9 +176,13 @@ class RoutedExperts(FeedForward):
             ops.moe_gemm_tc(xs, self.w_gate_up, mid, group_offsets=offsets, active=active,
                             tile_map=tiles, rows=R, glu=True, act=self.act, act_alpha=self.act_alpha,
                             act_limit=self.act_limit, tokens_per_tile=ntok)
+            # the down projection takes wider token tiles when experts are busy enough
+            ntok2 = ops.tc_tokens_per_tile(R, self.E, wide=True)
+            if ntok2 != ntok:
+                tiles = ops.moe_tile_map(offsets, active, R, self.E, ntok2, ctx.workspace, tag=".wide")
             ops.moe_gemm_tc(mid, self.w_down, parts, group_offsets=offsets, active=active,
                             tile_map=tiles, c_rows=sorted_route, row_scale=route_weight, rows=R,
-                            tokens_per_tile=ntok)
+                            tokens_per_tile=ntok2)
             return
         if ctx.dtype == torch.bfloat16 and ops.skinny_gemm_takes(x, self.w_gate_up, mid) \
                 and ops.skinny_gemm_takes(mid, self.w_down, parts):

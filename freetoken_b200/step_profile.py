@@ -18,7 +18,7 @@ import numpy as np
 import torch
 from torch.profiler import ProfilerActivity, profile
 
-from .benchmark import BENCH_CONFIG
+from .benchmark import BENCH_CONFIG, bench_random_options
 from .engine import Engine, EngineArgs, StepEntry
 
 
@@ -34,7 +34,7 @@ def main(argv=None) -> int:
     cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], a.context + 256)
     engine = Engine.from_config(cfg, 0, EngineArgs(
         dtype="bfloat16", page_size=64, max_tokens=a.batch * (a.context + 128) + a.context + 64,
-        max_running_requests=a.batch + 1))
+        max_running_requests=a.batch + 1), random_options=bench_random_options())
     rng = np.random.default_rng(0)
     V = cfg["vocab_size"]
     ids = [f"d{i}" for i in range(a.batch)]

@@ -35,8 +35,23 @@ class RandomOptions:
     matrix_std: Optional[float] = None
     norm_std: Optional[float] = None
     router_bias_std: Optional[float] = None
+    # Matrices that write into the residual stream (attention output, expert down
+    # projection; tag "residual_out") are matrices too, times this factor: the
+    # usual 1/sqrt(2 * layers) of residual networks.  Without it a deep random
+    # model's hidden states are dominated by what the layers add, the tokens of a
+    # prompt look alike to the router and a few experts get all of them - unlike a
+    # trained model, whose routing is balanced.
+    residual_out_scale: Optional[float] = None
+    embedding_std: Optional[float] = None      # the token embedding (tag "embedding"); default: as matrices
 
     def std_for(self, spec: TensorSpec) -> float:
+        if spec.tag == "residual_out":
+            base = spec.init.std if self.matrix_std is None else self.matrix_std
+            return base * (1.0 if self.residual_out_scale is None else self.residual_out_scale)
+        if spec.tag == "embedding":
+            if self.embedding_std is not None:
+                return self.embedding_std
+            return spec.init.std if self.matrix_std is None else self.matrix_std
         override = {
             "matrix": self.matrix_std,
             "norm": self.norm_std,

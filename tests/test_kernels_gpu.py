@@ -188,7 +188,8 @@ def _grouped_case(E, k, T, seed=0):
 @pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "skinny", "tc"])
 @pytest.mark.parametrize("E,k,T,H,I,act", [(4, 2, 5, 64, 32, "silu"), (8, 3, 19, 96, 48, "swigluoai"),
                                            (16, 4, 150, 128, 80, "silu"), (3, 1, 40, 40, 24, "silu"),
-                                           (8, 2, 700, 264, 200, "silu")])
+                                           (8, 2, 700, 264, 200, "silu"),
+                                           (4, 2, 650, 136, 72, "silu")])     # 325 rows per expert: wide tiles
 def test_expert_gemms(kernel, E, k, T, H, I, act):
     """gate_up + GLU, then down with the route weight, against a per-route loop."""
     o = ops()
@@ -212,8 +213,11 @@ def test_expert_gemms(kernel, E, k, T, H, I, act):
         tiles = o.moe_tile_map(offsets, active, R, E, ntok, Workspace(DEV))
         o.moe_gemm_tc(xs, w1, mid, group_offsets=offsets, active=active, tile_map=tiles, rows=R,
                       glu=True, act=act, tokens_per_tile=ntok)
+        ntok2 = o.tc_tokens_per_tile(R, E, wide=True)
+        if ntok2 != ntok:
+            tiles = o.moe_tile_map(offsets, active, R, E, ntok2, Workspace(DEV), tag=".wide")
         o.moe_gemm_tc(mid, w2, parts, group_offsets=offsets, active=active, tile_map=tiles,
-                      c_rows=sorted_route, row_scale=rw, rows=R, tokens_per_tile=ntok)
+                      c_rows=sorted_route, row_scale=rw, rows=R, tokens_per_tile=ntok2)
         torch.cuda.synchronize()
         o.check_tc_status(DEV)
     elif kernel == "skinny":
