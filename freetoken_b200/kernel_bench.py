@@ -75,9 +75,9 @@ def lm_head(sets: int = 2):
     return (lambda i: ops.skinny_gemm(x, w[i % sets], out)), V * H * 2, 0.0, "hbm"
 
 
-def moe_gemm_tc(sets: int = 2):
-    """Prefill: 256 tokens x 8 routes over 32 experts (64 rows each)."""
-    E, T, k = 32, 256, 8
+def moe_gemm_tc(sets: int = 1):
+    """Prefill: 512 tokens x 8 routes over 64 experts (64 rows each), 1.8 GB of weights."""
+    E, T, k = 64, 512, 8
     w1 = [torch.randn(E, 2 * I, H, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
     w2 = [torch.randn(E, H, I, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
     x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
@@ -91,12 +91,14 @@ def moe_gemm_tc(sets: int = 2):
     rw = torch.rand(R, device=DEV)
     ntok = ops.tc_tokens_per_tile(R, E)
     tiles = ops.moe_tile_map(offsets, active, R, E, ntok, ws)
+    ntok2 = ops.tc_tokens_per_tile(R, E, wide=True)
+    tiles2 = tiles if ntok2 == ntok else ops.moe_tile_map(offsets, active, R, E, ntok2, ws, tag=".wide")
 
     def run(i):
         ops.moe_gemm_tc(xs, w1[i % sets], mid, group_offsets=offsets, active=active, tile_map=tiles, rows=R,
                         glu=True, tokens_per_tile=ntok)
-        ops.moe_gemm_tc(mid, w2[i % sets], parts, group_offsets=offsets, active=active, tile_map=tiles,
-                        c_rows=route, row_scale=rw, rows=R, tokens_per_tile=ntok)
+        ops.moe_gemm_tc(mid, w2[i % sets], parts, group_offsets=offsets, active=active, tile_map=tiles2,
+                        c_rows=route, row_scale=rw, rows=R, tokens_per_tile=ntok2)
     return run, busy * 3 * I * H * 2, 2.0 * R * 3 * I * H, "hbm"
 
 
