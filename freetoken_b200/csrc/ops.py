@@ -442,13 +442,29 @@ def attn_decode_takes(q: torch.Tensor, head_dim: int) -> bool:
 
 
 def decode_splits(n_rows: int, num_kv_heads: int, group: int, max_kv_len: int, sms: int):
-    """``(splits, keys per split)``: enough CTAs to fill the SMs twice, whole 64-key tiles."""
+    """``(splits, keys per split)``, whole 64-key tiles per split.
+
+    Two CTAs of the decode kernel fit an SM and a launch takes as long as its
+    rounds of CTAs: rounds x (tiles per split + a CTA's fixed cost, about three
+    tiles' worth: query load, pipeline fill, partial write and its merge).  The
+    split count with the least such time is taken, the smaller one on a tie -
+    not just "enough CTAs to fill the SMs", which leaves a second round nearly
+    empty at some sizes."""
     base = max(1, n_rows * num_kv_heads * (-(-group // 16)))
     tiles = max(1, -(-max_kv_len // 64))
-    splits = min(max(1, -(-2 * sms // base)), tiles, 64)
-    split_keys = -(-tiles // splits) * 64
-    splits = -(-tiles * 64 // split_keys)
-    return splits, split_keys
+    slots = 2 * sms
+    best, best_cost = 1, None
+    for want in range(1, min(tiles, 64) + 1):
+        per = -(-tiles // want)
+        splits = -(-tiles // per)
+        if splits != want:
+            continue                      # the same split as a smaller request
+        rounds = -(-base * splits // slots)
+        cost = rounds * (per + 3)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = splits, cost
+    per = -(-tiles // best)
+    return -(-tiles // per), per * 64
 
 
 def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,

@@ -9,7 +9,7 @@ repetitions so that no repetition finds it in L2.
 
 Kernels: ``expert_gemv`` (decode experts, weight-streaming mma.sync kernel),
 ``lm_head`` (the same kernel, dense, float32 result), ``moe_gemm_tc`` (prefill
-experts on tcgen05/TMEM with TMA), ``attn_decode``, ``attn_prefill`` (mma.sync), ``attn_prefill_tc`` (tcgen05/TMEM, TMA-fed; ``_8k``: a
+experts on tcgen05/TMEM with TMA), ``attn_decode`` (64 rows x 2,048 keys; ``_32k``: 8 rows x 32,768 keys), ``attn_prefill`` (mma.sync), ``attn_prefill_tc`` (tcgen05/TMEM, TMA-fed; ``_8k``: a
 8,192-token prompt),
 ``router`` (float32 router logits + top-k for a decode batch).
 """
@@ -111,8 +111,7 @@ def _kv(batch: int, ctx: int, sets: int):
     return kv, table
 
 
-def attn_decode(sets: int = 2):
-    B, ctx = 64, 2048
+def attn_decode(sets: int = 2, B: int = 64, ctx: int = 2048):
     kv, table = _kv(B, ctx, sets)
     q = torch.randn(B, NQ * D, device=DEV, dtype=torch.bfloat16)
     out = torch.empty_like(q)
@@ -123,6 +122,11 @@ def attn_decode(sets: int = 2):
     def run(i):
         ops.attn_decode(q, out, kv[i % sets], None, B, pos, seg, table, NQ, NKV, D, D ** -0.5, None, ctx, ws)
     return run, B * ctx * 2 * NKV * D * 2, 4.0 * B * NQ * D * ctx, "hbm"
+
+
+def attn_decode_32k():
+    """8 decode rows with 32,768-token contexts (1.07 GB of K/V)."""
+    return attn_decode(sets=1, B=8, ctx=32768)
 
 
 def attn_prefill(sets: int = 1, tc: bool = False, T: int = 2048):
@@ -171,7 +175,7 @@ def router(sets: int = 8):
 
 KERNELS: Dict[str, Callable[[], Tuple[Callable[[int], None], int, float, str]]] = {
     "expert_gemv": expert_gemv, "lm_head": lm_head, "moe_gemm_tc": moe_gemm_tc,
-    "attn_decode": attn_decode, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
+    "attn_decode": attn_decode, "attn_decode_32k": attn_decode_32k, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
     "attn_prefill_8k": attn_prefill_8k, "attn_prefill_tc_8k": attn_prefill_tc_8k, "router": router,
 }
 
