@@ -78,10 +78,27 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
   const __nv_bfloat16* vbase = kbase + a.kv_stride;
   const int ntiles = k_end > k_begin ? (k_end - k_begin + TILE - 1) / TILE : 0;
 
+  // A tile lies inside one page when the page size is a multiple of the tile
+  // (tiles start at multiples of 64): one table lookup per tile; otherwise every
+  // key row looks its page up.
+  const bool tile_in_page = (a.P % TILE) == 0;
   auto load_tile = [&](int tile, int stage) {
     const int j0 = k_begin + tile * TILE;
     __nv_bfloat16* dk = sK + stage * TILE * LD;
     __nv_bfloat16* dv = sV + stage * TILE * LD;
+    if (tile_in_page) {
+      const size_t page_off = (size_t)table[j0 / a.P] * a.page_stride + (size_t)(j0 % a.P) * D;
+      const int last = pos - j0;                      // rows past the end repeat a valid key (masked later)
+#pragma unroll
+      for (int i = 0; i < TILE * CH / 128; ++i) {
+        const int idx = tid + 128 * i;
+        const int r = idx / CH, c = idx % CH;
+        const size_t off = page_off + (size_t)min(r, last) * D + c * 8;
+        cp_async16(dk + r * LD + c * 8, kbase + off);
+        cp_async16(dv + r * LD + c * 8, vbase + off);
+      }
+      return;
+    }
     for (int idx = tid; idx < TILE * CH; idx += 128) {
       const int r = idx / CH, c = idx % CH;
       const int j = min(j0 + r, pos);               // rows past the end repeat a valid key (masked later)
@@ -154,7 +171,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      // The running max only moves when it would grow by more than 2^8: below that
+      // exp2(s - max) stays far inside float32 and bfloat16 range and the rescale of
+      // the accumulator (64 multiplies a thread) is skipped.  The softmax is the same
+      // function of the scores whichever offset is subtracted.
+      const float mn0 = mx0 > m0 + 8.f ? mx0 : m0, mn1 = mx1 > m1 + 8.f ? mx1 : m1;
       const float al0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - mn0);
       const float al1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - mn1);
       const float base0 = (mn0 == -INFINITY) ? 0.f : mn0, base1 = (mn1 == -INFINITY) ? 0.f : mn1;
@@ -175,12 +196,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
       sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
       l0 = l0 * al0 + sum0;
       l1 = l1 * al1 + sum1;
+      if (__any_sync(0xffffffffu, mn0 != m0 || mn1 != m1)) {
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+          o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
+        }
+      }
       m0 = mn0;
       m1 = mn1;
-#pragma unroll
-      for (int n = 0; n < D / 8; ++n) {
-        o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
-      }
       // A fragment of P for k16 = 16 keys: {tile0 rows g, tile0 rows g+8, tile1 rows g, tile1 rows g+8}
       const unsigned pa[4] = {pf[0], pf[1], pf[2], pf[3]};
 #pragma unroll
