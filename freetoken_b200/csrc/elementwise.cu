@@ -294,6 +294,19 @@ __device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch /*
   b = scratch[65];
 }
 
+// 8 consecutive floats (norm weights, cos / sin): two 16-byte loads when the
+// address allows it
+__device__ __forceinline__ void load8w(const float* p, float (&v)[8]) {
+  if (((uintptr_t)p & 15) == 0) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = p[i];
+  }
+}
+
 // grid (tokens, parts): the blocks of a token split its heads between them;
 // with the per-layer norm every block sums the whole q and k rows itself (a
 // few KB from L2) so that no block waits for another.
@@ -359,18 +372,25 @@ __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
       const int i0 = ci * 8, i1 = i0 + half;
       Chunk8 x0 = load8(src + i0), x1 = load8(src + i1);
       if (a.norm_mode) {
+        float w0[8], w1[8];
+        load8w(nw + wbase + i0, w0);
+        load8w(nw + wbase + i1, w1);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          x0.v[i] = x0.v[i] * inv * (nw[wbase + i0 + i] + one);
-          x1.v[i] = x1.v[i] * inv * (nw[wbase + i1 + i] + one);
+          x0.v[i] = x0.v[i] * inv * (w0[i] + one);
+          x1.v[i] = x1.v[i] * inv * (w1[i] + one);
         }
       }
-      Chunk8 y0, y1;
+      Chunk8 y0 = x0, y1 = x1;
+      if (cs) {
+        float c[8], sn[8];
+        load8w(cs + i0, c);
+        load8w(cs + half + i0, sn);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float c = cs ? cs[i0 + i] : 1.f, sn = cs ? cs[half + i0 + i] : 0.f;
-        y0.v[i] = x0.v[i] * c - x1.v[i] * sn;
-        y1.v[i] = x1.v[i] * c + x0.v[i] * sn;
+        for (int i = 0; i < 8; ++i) {
+          y0.v[i] = x0.v[i] * c[i] - x1.v[i] * sn[i];
+          y1.v[i] = x1.v[i] * c[i] + x0.v[i] * sn[i];
+        }
       }
       store8(dst + i0, y0);
       store8(dst + i1, y1);
@@ -378,8 +398,10 @@ __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
       const int i0 = (ci + hc) * 8;               // pieces beyond the rotary span
       Chunk8 x0 = load8(src + i0);
       if (a.norm_mode) {
+        float w0[8];
+        load8w(nw + wbase + i0, w0);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) x0.v[i] = x0.v[i] * inv * (nw[wbase + i0 + i] + one);
+        for (int i = 0; i < 8; ++i) x0.v[i] = x0.v[i] * inv * (w0[i] + one);
       }
       store8(dst + i0, x0);
     }
