@@ -209,3 +209,48 @@ def test_a_stop_string_in_the_newest_text_stops_the_request():
         run_step(sched, cache, token_of=lambda r: next(out))
     r = sched.finished[0]
     assert r.output == [1, 3, 4] and r.finish_reason == "stop"     # "a EN" + "D " holds "END"
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_planning_one_step_ahead_gives_the_same_outputs_as_the_synchronous_loop(seed):
+    """A stand-in model whose next token is a function of the request and of how
+    many tokens it has: the loop that plans step N+1 before it records step N
+    must end with the same outputs, finish reasons and an empty cache as the loop
+    that records each step at once - with stops that are only seen one step late."""
+    def workload():
+        rng = random.Random(seed)
+        sched, cache = make(num_pages=rng.randint(10, 24), page=rng.choice([2, 4, 8]),
+                            slots=rng.randint(1, 4), max_seq_len=64, budget=rng.randint(2, 12), eos=[0])
+        reqs = [req(f"r{i}", rng.randint(1, 30), max_tokens=rng.randint(1, 12), ignore_eos=rng.random() < 0.3)
+                for i in range(10)]
+        return sched, cache, reqs
+
+    def token_of(r, n_out):
+        return (hash((r.id, n_out, seed)) % 7)          # 0 is the EOS: about one token in seven stops
+
+    def run(ahead: bool):
+        sched, cache, reqs = workload()
+        for r in reqs:
+            sched.submit(r)
+        inflight = None                                   # (plan, tokens) of the step not yet recorded
+        steps = 0
+        while sched.has_work() or inflight is not None:
+            steps += 1
+            assert steps < 2000
+            if not ahead and inflight is not None:
+                sched.complete(*inflight)
+                inflight = None
+            plan = sched.plan()
+            for e in plan:
+                cache.grow(e.request.id, cache.length(e.request.id) + len(e.tokens))
+                cache.advance(e.request.id, len(e.tokens))
+            # the token a sampling entry yields: by how many tokens the request will have then
+            tokens = [token_of(e.request, len(e.request.output) + e.request.inflight - 1) for e in plan if e.samples]
+            if inflight is not None:
+                sched.complete(*inflight)
+            inflight = (plan, tokens) if plan else None
+            sched.check_integrity()
+        assert cache.free_pages() == cache.total_pages()
+        return {r.id: (tuple(r.output), r.finish_reason) for r in reqs}
+
+    assert run(ahead=True) == run(ahead=False)
