@@ -11,7 +11,9 @@ Kernels: ``expert_gemv`` (decode experts, weight-streaming mma.sync kernel),
 ``lm_head`` (the same kernel, dense, float32 result), ``moe_gemm_tc`` (prefill
 experts on tcgen05/TMEM with TMA), ``attn_decode`` (64 rows x 2,048 keys; ``_32k``: 8 rows x 32,768 keys), ``attn_prefill`` (mma.sync), ``attn_prefill_tc`` (tcgen05/TMEM, TMA-fed; ``_8k``: a
 8,192-token prompt),
-``router`` (float32 router logits + top-k for a decode batch).
+``router`` (float32 router logits + top-k for a decode batch); ``*_flashinfer``: the same
+attention shapes through FlashInfer's trtllm-gen kernels (the reference's backend on
+this GPU), as a comparison point.
 """
 
 from __future__ import annotations
@@ -159,6 +161,53 @@ def attn_prefill_8k():
     return attn_prefill(T=8192)
 
 
+# ---- the same shapes through FlashInfer's trtllm-gen kernels (sm_100a cubins shipped
+# with the flashinfer_cubin package): the reference's attention backend on this GPU
+# (python/freetoken/attention/trtllm.py:62-100).  A comparison point only: nothing of
+# the engine calls them.
+def _flashinfer():
+    try:
+        import flashinfer
+        return flashinfer
+    except Exception as exc:           # not installed, or its launcher cannot be built here
+        raise SystemExit(json.dumps({"unavailable": f"flashinfer does not import: {exc!r}"}))
+
+
+def attn_decode_flashinfer(B: int = 64, ctx: int = 2048):
+    fi = _flashinfer()
+    kv, table = _kv(B, ctx, 2)
+    q = torch.randn(B, NQ, D, device=DEV, dtype=torch.bfloat16)
+    seq = torch.full((B,), ctx, dtype=torch.int32, device=DEV)
+    work = torch.zeros(256 << 20, dtype=torch.uint8, device=DEV)
+
+    def run(i):
+        fi.decode.trtllm_batch_decode_with_kv_cache(q, (kv[i % 2][0], kv[i % 2][1]), work, table, seq, ctx,
+                                                    bmm1_scale=D ** -0.5, bmm2_scale=1.0)
+    return run, B * ctx * 2 * NKV * D * 2, 4.0 * B * NQ * D * ctx, "hbm"
+
+
+def attn_decode_32k_flashinfer():
+    return attn_decode_flashinfer(8, 32768)
+
+
+def attn_prefill_flashinfer(T: int = 2048):
+    fi = _flashinfer()
+    kv, table = _kv(1, T, 1)
+    q = torch.randn(T, NQ, D, device=DEV, dtype=torch.bfloat16)
+    i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
+    seq, cu = i32([T]), i32([0, T])
+    work = torch.zeros(256 << 20, dtype=torch.uint8, device=DEV)
+
+    def run(i):
+        fi.prefill.trtllm_batch_context_with_kv_cache(q, (kv[0][0], kv[0][1]), work, table, seq, T, T,
+                                                      D ** -0.5, 1.0, 1, cu, cu)
+    return run, 0, 4.0 * NQ * D * (T * (T + 1) / 2), "tensor"
+
+
+def attn_prefill_8k_flashinfer():
+    return attn_prefill_flashinfer(8192)
+
+
 def router(sets: int = 8):
     E, T, k = 256, 8, 8
     w = [torch.randn(E, H, device=DEV) * 0.02 for _ in range(sets)]
@@ -177,6 +226,8 @@ KERNELS: Dict[str, Callable[[], Tuple[Callable[[int], None], int, float, str]]] 
     "expert_gemv": expert_gemv, "lm_head": lm_head, "moe_gemm_tc": moe_gemm_tc,
     "attn_decode": attn_decode, "attn_decode_32k": attn_decode_32k, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
     "attn_prefill_8k": attn_prefill_8k, "attn_prefill_tc_8k": attn_prefill_tc_8k, "router": router,
+    "attn_decode_flashinfer": attn_decode_flashinfer, "attn_decode_32k_flashinfer": attn_decode_32k_flashinfer,
+    "attn_prefill_flashinfer": attn_prefill_flashinfer, "attn_prefill_8k_flashinfer": attn_prefill_8k_flashinfer,
 }
 
 
