@@ -341,3 +341,14 @@ extern "C" int ft_attn_decode(const void* q, void* out, float* part_o, float* pa
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
+
+// The split merge alone, for partials another kernel wrote in the same layout.
+extern "C" int ft_attn_merge(const float* part_o, const float* part_ml, void* out, const int* rows,
+                             int n_rows, int nq, int d, int splits, cudaStream_t stream) {
+  if (n_rows <= 0 || splits < 1) return FT_OK;
+  dim3 grid(n_rows, nq);
+  launch_pdl(attn_merge_kernel, grid, dim3(128), 0, stream, part_o, part_ml, (__nv_bfloat16*)out, rows, nq, d,
+             splits);
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}

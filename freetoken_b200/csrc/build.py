@@ -41,6 +41,7 @@ LIBRARIES: Dict[str, str] = {
     "sampling": "sampling.cu",
     "skinny_gemm": "skinny_gemm.cu",
     "attention_decode": "attention_decode.cu",
+    "attention_decode_tma": "attention_decode_tma.cu",
     "attention_prefill": "attention_prefill.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "moe_gemm_tc": "moe_gemm_tc.cu",

@@ -441,6 +441,11 @@ def attn_decode_takes(q: torch.Tensor, head_dim: int) -> bool:
     return q.dtype == torch.bfloat16 and head_dim in DECODE_HEAD_DIMS
 
 
+# Decode attention with K/V tiles fetched by TMA where the shapes allow it
+# (FREETOKEN_DECODE_TMA=0: always the cp.async kernel).
+DECODE_TMA = os.environ.get("FREETOKEN_DECODE_TMA", "1") not in ("", "0")
+
+
 def decode_splits(n_rows: int, num_kv_heads: int, group: int, max_kv_len: int, sms: int):
     """``(splits, keys per split)``, whole 64-key tiles per split.
 
@@ -488,6 +493,29 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
     if splits > 1:
         part_o = workspace.get("attn.part_o", (n_rows, num_heads, splits, head_dim), torch.float32)
         part_ml = workspace.get("attn.part_ml", (n_rows, num_heads, splits, 2), torch.float32)
+    if DECODE_TMA and head_dim in (64, 128) and kv_pages.shape[3] % 64 == 0 \
+            and kv_pages.stride(4) == 1 and kv_pages.stride(3) == head_dim:
+        # K and V tiles by TMA: a tile lies inside one page
+        lib = build.load("attention_prefill_tc")
+
+        def make_kv(dst):
+            mk = lib.ft_attn_tc_kv_map
+            mk.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_longlong] * 7
+            mk.restype = ctypes.c_int
+            return mk(dst, kv_pages.data_ptr(), kv_pages.shape[1], kv_pages.shape[2], kv_pages.shape[3],
+                      head_dim, kv_pages.stride(2), kv_pages.stride(1), kv_pages.stride(0))
+        map_kv = _attn_tc_map("kv", (kv_pages.data_ptr(),) + tuple(kv_pages.shape) + tuple(kv_pages.stride()),
+                              make_kv)
+        f = _fn("attention_decode_tma", "ft_attn_decode_tma", "p p p p p p p p p p i i i i i i i i i f")
+        _check(f(ctypes.cast(map_kv, ctypes.c_void_p), _ptr(q), _ptr(out), _ptr(part_o), _ptr(part_ml),
+                 _ptr(rows), _ptr(token_pos), _ptr(token_seg), _ptr(block_table), _ptr(tc_status(q.device)),
+                 num_heads, num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1],
+                 int(window or 0), n_rows, splits, split_keys, float(scale), _stream()), "attn_decode_tma")
+        if splits > 1:
+            fm = _fn("attention_decode", "ft_attn_merge", "p p p p i i i i")
+            _check(fm(_ptr(part_o), _ptr(part_ml), _ptr(out), _ptr(rows), n_rows, num_heads, head_dim,
+                      splits, _stream()), "attn_merge")
+        return
     f = _fn("attention_decode", "ft_attn_decode", "p p p p p p p p p q q i i i i i i i i i f")
     _check(f(_ptr(q), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(kv_pages), _ptr(rows),
              _ptr(token_pos), _ptr(token_seg), _ptr(block_table), kv_pages.stride(1),

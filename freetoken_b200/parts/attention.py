@@ -95,8 +95,9 @@ class PagedAttention(Mixer):
 
     def libraries(self, dtype) -> List[str]:
         fast = ["attention_decode", "attention_prefill"] if dtype == torch.bfloat16 else []
-        if fast and self.d in (64, 128) and self.window is None:
-            fast.append("attention_prefill_tc")
+        if fast and self.d in (64, 128):
+            # TMA-fed kernels (the prefill one also builds the tensor maps both use)
+            fast += ["attention_prefill_tc", "attention_decode_tma"]
         return ["elementwise", "attention_simt"] + fast + linear.libraries(dtype)
 
     # ---- forward ----------------------------------------------------------------

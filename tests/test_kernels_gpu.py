@@ -467,6 +467,10 @@ DECODE_CASES = [
     (12, 2, 64, 16, [700], None, (0, 333)),               # one row: many splits
     (40, 2, 64, 32, [130, 64], 100, None),                # group of 20: two head tiles
     (3, 3, 32, 8, [300, 5, 77], None, None),              # group of 1
+    # pages of a multiple of 64 and head size 64 / 128: tiles fetched by TMA
+    (8, 2, 64, 128, [500, 64, 127, 128], None, (0, 70)),   # two tiles in a page
+    (12, 4, 128, 64, [900, 3], 150, None),                # window over three pages
+    (40, 2, 64, 64, [130, 64], 100, None),                # group of 20: two head tiles
 ]
 
 
@@ -482,6 +486,17 @@ def test_attn_decode(nq, nkv, d, P, positions, window, standout):
                   max(positions) + 1, Workspace(DEV))
     want = _attn_ref(q, kv, pos, seg, table, nq, nkv, d, P, scale, window)
     assert torch.allclose(out.float().cpu(), want, **TOL["bfloat16"])
+    o.check_tc_status(DEV)
+    if d in (64, 128) and P % 64 == 0:
+        # the same through the cp.async kernel
+        out3 = torch.zeros_like(q)
+        o.DECODE_TMA = False
+        try:
+            o.attn_decode(q, out3, kv, None, len(positions), pos, seg, table, nq, nkv, d, scale, window,
+                          max(positions) + 1, Workspace(DEV))
+        finally:
+            o.DECODE_TMA = True
+        assert torch.allclose(out3.float().cpu(), want, **TOL["bfloat16"])
     # a subset of rows through the row list leaves the other rows alone
     if len(positions) > 1:
         rows = torch.tensor([len(positions) - 1], dtype=torch.int32, device=DEV)
