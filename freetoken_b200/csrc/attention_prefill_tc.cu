@@ -54,8 +54,13 @@ struct PrefillTcArgs {
   float scale_log2;          // sm_scale * log2(e)
 };
 
-template <int D>
+// HPC: query heads per CTA.  1: the CTA's 128 rows are 128 tokens of one head.
+// 2: they are 64 tokens of two heads that share a KV head (an even group size):
+// the K and V tiles a CTA fetches then serve two heads, which halves the
+// L2 -> shared memory traffic per product, the scarcer resource at this tile size.
+template <int D, int HPC>
 __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q,
+                                                                 const __grid_constant__ CUtensorMap tm_q2,
                                                                  const __grid_constant__ CUtensorMap tm_kv,
                                                                  PrefillTcArgs a) {
   constexpr int NB = D / 64;                 // 64-wide (128-byte) blocks per head
@@ -66,8 +71,9 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
 
   // the host lists 64-token tiles; a CTA takes an even one together with its successor
   const int tile_index = gridDim.x - 1 - blockIdx.x;     // backwards: most keys first
+  constexpr int TOK = AQ / HPC;                       // tokens per CTA
   const int q0 = a.tile_q0[tile_index];
-  if (q0 % AQ) return;
+  if (q0 % TOK) return;                               // HPC == 1: a CTA takes an even list tile and its successor
   const int seg = a.tile_seg[tile_index];
 
   extern __shared__ unsigned char smem_dyn[];
@@ -80,11 +86,11 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
   __shared__ volatile int gave_up;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y;
+  const int head = blockIdx.y * HPC;                  // first of the CTA's heads (same KV head: G % HPC == 0)
   const int kvh = head / (a.nq / a.nkv);
   const int seg_begin = a.seg_q_start[seg];
   const int n = a.seg_q_start[seg + 1] - seg_begin;
-  const int rows = min(AQ, n - q0);
+  const int rows = min(TOK, n - q0);                  // tokens this CTA really has
   const int tok0 = seg_begin + q0;
   const int pos_first = a.seg_pos0[seg] + q0;
   const int ntiles = (pos_first + rows - 1) / AK + 1;
@@ -115,7 +121,11 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     if (lane == 0) {
       mbar_expect_tx(&q_full, Q_BYTES);
 #pragma unroll
-      for (int h = 0; h < NB; ++h) tma_load_2d(sQ + h * QB, &tm_q, head * D + h * 64, tok0, &q_full);
+      for (int h = 0; h < NB; ++h)
+#pragma unroll
+        for (int hh = 0; hh < HPC; ++hh)      // head hh fills rows hh*TOK .. of every 64-wide block
+          tma_load_2d(sQ + h * QB + hh * TOK * 128, HPC == 1 ? &tm_q : &tm_q2, (head + hh) * D + h * 64, tok0,
+                      &q_full);
       const int* table = a.block_table + (size_t)seg * a.table_width;
       // K runs one tile ahead of V: K_j is wanted a whole softmax earlier than V_j
       int k_issued = 0, v_issued = 0;
@@ -220,7 +230,8 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     // softmax: TMEM lane = query row; this warp may touch lanes 32*(warp%4) .. +31
     const int lane_base = (warp & 3) * 32;
     const int r = lane_base + lane;
-    const int my_pos = pos_first + r;
+    const int my_tok = r % TOK, my_head = head + r / TOK;
+    const int my_pos = pos_first + my_tok;
     const unsigned lane_bits = (unsigned)lane_base << 16;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
@@ -310,13 +321,13 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = a.out + ((size_t)(tok0 + r) * a.nq + head) * D;
+      __nv_bfloat16* orow = a.out + ((size_t)(tok0 + my_tok) * a.nq + my_head) * D;
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 32) {
         unsigned o[32];
         tc_ld32(tmem_o + lane_bits + c0, o);
         tc_ld_wait();
-        if (r < rows) {
+        if (my_tok < rows) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
             uint4 v;
@@ -354,21 +365,21 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int D>
-int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mkv, const PrefillTcArgs& a, int tiles,
-                      cudaStream_t stream) {
+template <int D, int HPC>
+int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mq2, const CUtensorMap& mkv,
+                      const PrefillTcArgs& a, int tiles, cudaStream_t stream) {
   constexpr int NB = D / 64;
   constexpr int K_BYTES = NB * AK * 128;
   const size_t smem = (size_t)NB * AQ * 128 + 4 * K_BYTES + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<D, HPC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid(tiles, a.nq);
-  attn_prefill_tc_kernel<D><<<grid, 192, smem, stream>>>(mq, mkv, a);
+  dim3 grid(tiles, a.nq / HPC);
+  attn_prefill_tc_kernel<D, HPC><<<grid, 192, smem, stream>>>(mq, mq2, mkv, a);
   return FT_OK;
 }
 
@@ -379,15 +390,18 @@ using namespace ft;
 extern "C" {
 
 // Tensor map over the bfloat16 query rows [rows, cols] (row stride in elements):
-// boxes of 128 rows by 64 columns in the 128-byte swizzle.  `out` receives 128 bytes.
-int ft_attn_tc_q_map(void* out, const void* base, long long rows, long long cols, long long row_stride) {
+// boxes of `box_rows` (128 or 64) rows by 64 columns in the 128-byte swizzle.
+// `out` receives 128 bytes.
+int ft_attn_tc_q_map(void* out, const void* base, long long rows, long long cols, long long row_stride,
+                     int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -201;
-  if ((cols & 7) || (row_stride & 7) || ((uintptr_t)base & 15)) return FT_ERR_SHAPE;
+  if ((cols & 7) || (row_stride & 7) || ((uintptr_t)base & 15) || (box_rows != AQ && box_rows != AQ / 2))
+    return FT_ERR_SHAPE;
   CUtensorMap map;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
-  cuuint32_t box[2] = {64, AQ};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t es[2] = {1, 1};
   CUresult rc = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, es,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -422,22 +436,32 @@ int ft_attn_tc_kv_map(void* out, const void* base, long long pages, long long nk
 
 // bfloat16; head_dim 64 or 128; page size a multiple of 64; no window.
 // tile_seg / tile_q0 list the query tiles (64 tokens) of the segments to
-// process; a CTA takes an even tile with its successor.
-int ft_attn_prefill_tc(const void* map_q, const void* map_kv, void* out, const int* tile_seg,
+// process.  With an even number of query heads per KV head a CTA takes one tile
+// and two heads (`map_q2`: boxes of 64 rows); otherwise an even tile with its
+// successor and one head (`map_q`: boxes of 128 rows).
+int ft_attn_prefill_tc(const void* map_q, const void* map_q2, const void* map_kv, void* out, const int* tile_seg,
                        const int* tile_q0, const int* seg_q_start, const int* seg_pos0,
                        const int* block_table, int* status, int nq, int nkv, int d, int P,
                        int table_width, int tiles, float scale, cudaStream_t stream) {
   if (tiles <= 0) return FT_OK;
   if (nkv <= 0 || nq % nkv || P % AK) return FT_ERR_SHAPE;
-  CUtensorMap mq, mkv;
+  CUtensorMap mq, mq2, mkv;
   memcpy(&mq, map_q, sizeof(mq));
+  memcpy(&mq2, map_q2, sizeof(mq2));
   memcpy(&mkv, map_kv, sizeof(mkv));
+  const bool pair = ((nq / nkv) % 2) == 0;
   PrefillTcArgs a{(__nv_bfloat16*)out, tile_seg, tile_q0, seg_q_start, seg_pos0, block_table, status,
                   nq, nkv, P, table_width, scale * 1.4426950408889634f};
   int rc;
   switch (d) {
-    case 64: rc = launch_prefill_tc<64>(mq, mkv, a, tiles, stream); break;
-    case 128: rc = launch_prefill_tc<128>(mq, mkv, a, tiles, stream); break;
+    case 64:
+      rc = pair ? launch_prefill_tc<64, 2>(mq, mq2, mkv, a, tiles, stream)
+                : launch_prefill_tc<64, 1>(mq, mq2, mkv, a, tiles, stream);
+      break;
+    case 128:
+      rc = pair ? launch_prefill_tc<128, 2>(mq, mq2, mkv, a, tiles, stream)
+                : launch_prefill_tc<128, 1>(mq, mq2, mkv, a, tiles, stream);
+      break;
     default: return FT_ERR_SHAPE;
   }
   if (rc != FT_OK) return rc;

@@ -592,11 +592,13 @@ def attn_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
     lib = build.load("attention_prefill_tc")
     T, cols = q.shape
 
-    def make_q(dst):
-        f = lib.ft_attn_tc_q_map
-        f.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_longlong] * 3
-        f.restype = ctypes.c_int
-        return f(dst, q.data_ptr(), T, cols, q.stride(0))
+    def make_q(box_rows):
+        def make(dst):
+            f = lib.ft_attn_tc_q_map
+            f.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_longlong] * 3 + [ctypes.c_int]
+            f.restype = ctypes.c_int
+            return f(dst, q.data_ptr(), T, cols, q.stride(0), box_rows)
+        return make
 
     def make_kv(dst):
         f = lib.ft_attn_tc_kv_map
@@ -605,12 +607,14 @@ def attn_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
         return f(dst, kv_pages.data_ptr(), kv_pages.shape[1], kv_pages.shape[2], kv_pages.shape[3],
                  head_dim, kv_pages.stride(2), kv_pages.stride(1), kv_pages.stride(0))
 
-    map_q = _attn_tc_map("q", (q.data_ptr(), T, cols, q.stride(0)), make_q)
+    map_q = _attn_tc_map("q", (q.data_ptr(), T, cols, q.stride(0)), make_q(128))
+    map_q2 = _attn_tc_map("q2", (q.data_ptr(), T, cols, q.stride(0)), make_q(64))
     map_kv = _attn_tc_map("kv", (kv_pages.data_ptr(),) + tuple(kv_pages.shape) + tuple(kv_pages.stride()),
                           make_kv)
     status = tc_status(q.device)
-    f = _fn("attention_prefill_tc", "ft_attn_prefill_tc", "p p p p p p p p p i i i i i i f")
-    _check(f(ctypes.cast(map_q, ctypes.c_void_p), ctypes.cast(map_kv, ctypes.c_void_p), _ptr(out),
+    f = _fn("attention_prefill_tc", "ft_attn_prefill_tc", "p p p p p p p p p p i i i i i i f")
+    _check(f(ctypes.cast(map_q, ctypes.c_void_p), ctypes.cast(map_q2, ctypes.c_void_p),
+             ctypes.cast(map_kv, ctypes.c_void_p), _ptr(out),
              _ptr(tile_seg), _ptr(tile_q0), _ptr(seg_q_start), _ptr(seg_pos0), _ptr(block_table),
              _ptr(status), num_heads, num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1],
              tile_seg.numel(), float(scale), _stream()), "attn_prefill_tc")
