@@ -90,7 +90,12 @@ def _run_generate(argv: Sequence[str]) -> int:
     sp = SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
                         ignore_eos=a.ignore_eos, max_tokens=a.max_tokens, seed=a.seed,
                         stop_strs=[x for x in a.stop if x], stop_token_ids=a.stop_token_id)
-    for prompt, result in zip(prompts, llm.generate(prompts, sp)):
+    try:
+        results = llm.generate(prompts, sp)
+    except ValueError as exc:           # e.g. text prompts or stop strings without a tokenizer
+        print(f"ft generate: {exc}", file=sys.stderr)
+        return 2
+    for prompt, result in zip(prompts, results):
         print(json.dumps({"prompt": prompt, **result}))
     return 0
 
