@@ -40,7 +40,7 @@ BENCH_CONFIG: Dict[str, Any] = dict(
 FAMILY_LAYERS = 62
 
 
-def bench_random_options():
+def bench_random_options(router_bias_std: Optional[float] = None):
     """Scales of the benchmark's random weights.  With every matrix ~N(0, 0.02^2) the
     hidden states of a prompt's tokens are dominated by what the layers add (the
     attention of a random model averages over the prefix), the router sees almost the
@@ -52,7 +52,8 @@ def bench_random_options():
     routes like the first one (256 of 256 experts touched, the busiest with under twice
     the mean load)."""
     from .weights import RandomOptions
-    return RandomOptions(embedding_std=1.0, residual_out_scale=(2.0 * FAMILY_LAYERS) ** -0.5)
+    return RandomOptions(embedding_std=1.0, residual_out_scale=(2.0 * FAMILY_LAYERS) ** -0.5,
+                         router_bias_std=router_bias_std)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -181,6 +182,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--points", default="1,64", help="further decode batch sizes")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--router-bias-std", type=float, default=None,
+                   help="spread of the random score-correction bias (skews which experts are popular)")
     return p
 
 
@@ -214,7 +217,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     peaks = load_peaks()
     t0 = time.time()
     llm = LLM("", a.dtype, config=cfg, use_dummy_weight=True, seed=a.seed,
-              dummy_weight_options=bench_random_options(),
+              dummy_weight_options=bench_random_options(a.router_bias_std),
               max_running_req=max_batch + 1, page_size=page, num_token_override=pool_tokens,
               max_extend_tokens=8192, max_seq_len_override=room + page)
     engine = llm.engine
@@ -263,11 +266,20 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     # ---- decode at each batch size -----------------------------------------
     def fill_contexts(batch: int) -> List[str]:
+        """Contexts of ``--context`` tokens by real prefill, in steps of at most 8,192 tokens
+        (several short requests per step, or a long one in portions)."""
         ids = [f"d{i}" for i in range(batch)]
-        per_step = max(1, 8192 // a.context)
-        for i in range(0, batch, per_step):
-            group = ids[i:i + per_step]
-            engine.step([StepEntry(r, rng.integers(0, V, a.context).tolist(), []) for r in group])
+        step_tokens = 8192
+        if a.context <= step_tokens:
+            per_step = max(1, step_tokens // a.context)
+            for i in range(0, batch, per_step):
+                group = ids[i:i + per_step]
+                engine.step([StepEntry(r, rng.integers(0, V, a.context).tolist(), []) for r in group])
+        else:
+            for r in ids:
+                for lo in range(0, a.context, step_tokens):
+                    n = min(step_tokens, a.context - lo)
+                    engine.step([StepEntry(r, rng.integers(0, V, n).tolist(), [])])
         return ids
 
     results: Dict[int, Dict[str, float]] = {}
