@@ -153,6 +153,37 @@ def prefill_flops(cfg: Dict[str, Any], layers: int, tokens: int) -> float:
     return layers * (per_token * tokens + attn) + 2 * V * H
 
 
+def equivalence(a) -> int:
+    """The float32 path against the bfloat16 path at real width: same seed, same
+    token ids, logits at 15 prompt positions and at 8 decoded tokens."""
+    import numpy as np
+    import torch
+
+    from .engine import Engine, EngineArgs, StepEntry
+
+    cfg = dict(BENCH_CONFIG)
+    cfg["num_hidden_layers"] = a.layers or 2
+    toks = np.random.default_rng(a.seed).integers(0, cfg["vocab_size"], 520).tolist()
+    want = list(range(0, 512, 37)) + [511]
+    logits = {}
+    for dtype in ("float32", "bfloat16"):
+        engine = Engine.from_config(cfg, a.seed, EngineArgs(dtype=dtype, page_size=64, max_tokens=1024,
+                                                            max_running_requests=2),
+                                    random_options=bench_random_options(a.router_bias_std))
+        rows = [engine.step([StepEntry("a", toks[:512], want)]).float().cpu()]
+        for t in toks[512:]:
+            rows.append(engine.step([StepEntry("a", [t], [0])]).float().cpu())
+        logits[dtype] = torch.cat(rows)
+        del engine
+        torch.cuda.empty_cache()
+    f, b = logits["float32"], logits["bfloat16"]
+    print(json.dumps({"equivalence": "float32 vs bfloat16", "layers": cfg["num_hidden_layers"],
+                      "positions": f.shape[0], "logit_max_abs": f.abs().max().item(),
+                      "max_abs_diff": (f - b).abs().max().item(), "mean_abs_diff": (f - b).abs().mean().item(),
+                      "argmax_agree": (f.argmax(-1) == b.argmax(-1)).float().mean().item()}))
+    return 0
+
+
 def reference_unavailable() -> str:
     """Why the reference arm cannot run: tried against ``baseline/_ref``."""
     ref = os.path.join(ROOT, "baseline", "_ref")
@@ -182,6 +213,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--points", default="1,64", help="further decode batch sizes")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--equivalence", action="store_true",
+                   help="instead of timing: the same random model (--layers, default 2) in float32 and in "
+                        "bfloat16 on one 512-token prompt and 8 decoded tokens; prints how far the logits differ")
     p.add_argument("--router-bias-std", type=float, default=None,
                    help="spread of the random score-correction bias (skews which experts are popular)")
     return p
@@ -198,6 +232,9 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     import numpy as np
     import torch
+
+    if a.equivalence:
+        return equivalence(a)
 
     from .csrc import ops
     from .engine import StepEntry
