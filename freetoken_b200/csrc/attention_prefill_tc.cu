@@ -293,19 +293,22 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       // P = exp2(s * scale - max), summed in float32, rounded to bfloat16 and written
       // over S: column c of the buffer holds keys 2c and 2c+1
       const float neg_m = -m_new;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // packed pairs: one fma.rn.f32x2 / add.f32x2 does two elements
+      const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nm2 = make_float2(neg_m, neg_m);
+      float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       unsigned pk[32];
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(lo[2 * c]), a.scale_log2, neg_m));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(lo[2 * c + 1]), a.scale_log2, neg_m));
-        const float p2 = fast_exp2(fmaf(__uint_as_float(hi[2 * c]), a.scale_log2, neg_m));
-        const float p3 = fast_exp2(fmaf(__uint_as_float(hi[2 * c + 1]), a.scale_log2, neg_m));
-        sum4[c & 3] += (p0 + p1) + (p2 + p3);
-        pk[c] = pack_bf16(p0, p1);
-        pk[16 + c] = pack_bf16(p2, p3);
+        const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(lo[2 * c]), __uint_as_float(lo[2 * c + 1])), sc2, nm2);
+        const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(hi[2 * c]), __uint_as_float(hi[2 * c + 1])), sc2, nm2);
+        const float2 p01 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
+        const float2 p23 = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
+        sum2[c & 3] = __fadd2_rn(sum2[c & 3], __fadd2_rn(p01, p23));
+        pk[c] = pack_bf16(p01.x, p01.y);
+        pk[16 + c] = pack_bf16(p23.x, p23.y);
       }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      const float2 s01 = __fadd2_rn(__fadd2_rn(sum2[0], sum2[1]), __fadd2_rn(sum2[2], sum2[3]));
+      const float sum = s01.x + s01.y;
       tc_st32(tmem_sj, pk);
       tc_st_wait();
       l += sum;
