@@ -13,7 +13,8 @@ experts on tcgen05/TMEM with TMA), ``attn_decode`` (64 rows x 2,048 keys; ``_32k
 8,192-token prompt),
 ``router`` (float32 router logits + top-k for a decode batch); ``*_flashinfer``: the same
 attention shapes through FlashInfer's trtllm-gen kernels (the reference's backend on
-this GPU), as a comparison point.
+this GPU), as a comparison point; ``peak_copy`` / ``peak_gemm``: a 1 GiB device copy and an
+8192^3 library bf16 product, the two roofline denominators measured in place.
 """
 
 from __future__ import annotations
@@ -208,6 +209,23 @@ def attn_prefill_8k_flashinfer():
     return attn_prefill_flashinfer(8192)
 
 
+# ---- the two denominators, measured the way the fallback figures were: a device-to-device
+# copy (read + write bytes over time) and a large library bf16 product
+def peak_copy():
+    n = 1 << 30
+    a = torch.empty(n, dtype=torch.uint8, device=DEV)
+    b = torch.empty(n, dtype=torch.uint8, device=DEV)
+    return (lambda i: b.copy_(a)), 2 * n, 0.0, "hbm"
+
+
+def peak_gemm():
+    n = 8192
+    a = torch.randn(n, n, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(n, n, device=DEV, dtype=torch.bfloat16)
+    c = torch.empty(n, n, device=DEV, dtype=torch.bfloat16)
+    return (lambda i: torch.matmul(a, b, out=c)), 0, 2.0 * n ** 3, "tensor"
+
+
 def router(sets: int = 8):
     E, T, k = 256, 8, 8
     w = [torch.randn(E, H, device=DEV) * 0.02 for _ in range(sets)]
@@ -226,6 +244,7 @@ KERNELS: Dict[str, Callable[[], Tuple[Callable[[int], None], int, float, str]]] 
     "expert_gemv": expert_gemv, "lm_head": lm_head, "moe_gemm_tc": moe_gemm_tc,
     "attn_decode": attn_decode, "attn_decode_32k": attn_decode_32k, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
     "attn_prefill_8k": attn_prefill_8k, "attn_prefill_tc_8k": attn_prefill_tc_8k, "router": router,
+    "peak_copy": peak_copy, "peak_gemm": peak_gemm,
     "attn_decode_flashinfer": attn_decode_flashinfer, "attn_decode_32k_flashinfer": attn_decode_32k_flashinfer,
     "attn_prefill_flashinfer": attn_prefill_flashinfer, "attn_prefill_8k_flashinfer": attn_prefill_8k_flashinfer,
 }
