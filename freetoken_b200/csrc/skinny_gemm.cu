@@ -199,7 +199,8 @@ int launch_nt(const SkinnyArgs& a, int nt, dim3 grid, cudaStream_t stream) {
   return FT_OK;
 }
 
-// Warps per block for a dense [N, K] weight: doubled from 4 while the launch
+// Warps per block for a dense [N, K] weight: 2 when there are blocks in plenty
+// anyway (measured 4 % faster on the head), else doubled from 4 while the launch
 // would hold fewer than about 20 warps per SM and a warp keeps at least 8
 // chunks of 32 k.  A function of the weight's shape only, so a token's result
 // does not depend on what else is in the batch.
@@ -207,6 +208,7 @@ static int dense_k_split(int N, int K) {
   const long long tiles = (N + 15) / 16;
   const int chunks = (K + 31) / 32;
   int ks = 4;
+  if (tiles * 2 >= 6000) return 2;      // blocks in plenty (the head): long streams per warp
   while (ks < 16 && tiles * ks < 3000 && chunks / (2 * ks) >= 8) ks *= 2;
   return ks;
 }
@@ -246,6 +248,7 @@ extern "C" int ft_skinny_gemm(const void* A, long long lda, const void* W,
     else rc = launch_nt<false, __nv_bfloat16, 4>(a, nt, grid, stream);
   } else if (c_dtype == FT_DTYPE_F32) {
     if (glu) rc = launch_nt<true, float, 4>(a, nt, grid, stream);
+    else if (ks == 2) rc = launch_nt<false, float, 2>(a, nt, grid, stream);
     else if (ks == 16) rc = launch_nt<false, float, 16>(a, nt, grid, stream);
     else if (ks == 8) rc = launch_nt<false, float, 8>(a, nt, grid, stream);
     else rc = launch_nt<false, float, 4>(a, nt, grid, stream);
