@@ -323,8 +323,17 @@ def main(argv: Optional[List[str]] = None) -> int:
     clocks_main: Dict[str, Any] = {}
     launches_main = 0
     touched_main: List[int] = []
+    context_build: Dict[str, Any] = {}
     for batch in batches:
+        torch.cuda.synchronize()
+        t_fill = time.time()
         ids = fill_contexts(batch)
+        torch.cuda.synchronize()
+        if batch == a.batch:
+            # wall time of building the contexts by real prefill (steps of at most 8,192 tokens)
+            fill_s = time.time() - t_fill
+            context_build = {"tokens": batch * a.context, "s": round(fill_s, 3),
+                             "tokens_per_s": round(batch * a.context / fill_s)}
         params = [greedy] * batch
         zeros = [0.0] * batch
 
@@ -407,6 +416,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         "points_roofline_frac": {f"decode_b{b}": results[b]["gbs"] / peaks["hbm_gbs"] for b in batches},
         "clocks": clocks_main,
         "prefill_clocks": prefill_clocks.summary(),
+        "context_build": context_build,
         "setup_s": round(build_s, 1),
     }
     print(json.dumps(line))
