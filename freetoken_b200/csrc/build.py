@@ -17,6 +17,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -141,8 +142,9 @@ def _compile(name: str, out: str, verbose_ptxas: bool = False) -> None:
         _say(text)
     # drop older builds of the same library
     folder = os.path.dirname(out)
+    stale = re.compile(rf"libft_{re.escape(name)}_[0-9a-f]{{16}}\.so$")   # not libft_<name>_<more>_...
     for f in os.listdir(folder):
-        if f.startswith(f"libft_{name}_") and f.endswith(".so") and os.path.join(folder, f) != out:
+        if stale.match(f) and os.path.join(folder, f) != out:
             try:
                 os.remove(os.path.join(folder, f))
             except OSError:
