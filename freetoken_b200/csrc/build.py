@@ -140,16 +140,23 @@ def _compile(name: str, out: str, verbose_ptxas: bool = False) -> None:
     os.replace(tmp, out)
     if verbose_ptxas:
         _say(text)
-    # drop older builds of the same library
-    folder = os.path.dirname(out)
-    stale = re.compile(rf"libft_{re.escape(name)}_[0-9a-f]{{16}}\.so$")   # not libft_<name>_<more>_...
+    drop_stale(os.path.dirname(out), name, out)
+    _say(f"built {os.path.basename(out)} in {time.time() - start:.1f} s")
+
+
+def drop_stale(folder: str, name: str, keep: str) -> List[str]:
+    """Remove older binaries of library ``name`` from ``folder`` (all but ``keep``);
+    a library whose name merely starts with ``name`` is someone else's."""
+    stale = re.compile(rf"libft_{re.escape(name)}_[0-9a-f]{{16}}\.so$")
+    removed = []
     for f in os.listdir(folder):
-        if stale.match(f) and os.path.join(folder, f) != out:
+        if stale.match(f) and os.path.join(folder, f) != keep:
             try:
                 os.remove(os.path.join(folder, f))
+                removed.append(f)
             except OSError:
                 pass
-    _say(f"built {os.path.basename(out)} in {time.time() - start:.1f} s")
+    return removed
 
 
 _loaded: Dict[str, ctypes.CDLL] = {}
