@@ -573,3 +573,15 @@ def test_attn_prefill_tc(nq, nkv, d, P, lens, standout):
     o.check_tc_status(DEV)
     want = _attn_ref(q, kv, pos, seg, table, nq, nkv, d, P, scale, None)
     assert torch.allclose(out.float().cpu(), want, **TOL["bfloat16"])
+
+
+def test_patch_tokens_copies_sampled_ids_into_the_next_steps_inputs():
+    o = ops()
+    ids = torch.arange(100, 120, dtype=torch.int32, device=DEV)
+    src = torch.tensor([7, 8, 999999, -3, 11], dtype=torch.int32, device=DEV)
+    rows = torch.tensor([0, 19, 5, 6, 7], dtype=torch.int32, device=DEV)
+    src_index = torch.tensor([4, 0, 2, 3, 1], dtype=torch.int32, device=DEV)
+    o.patch_tokens(ids, rows, src, src_index, 1000)
+    want = list(range(100, 120))
+    want[0], want[19], want[5], want[6], want[7] = 11, 7, 0, 0, 8     # ids outside the vocabulary become 0
+    assert ids.tolist() == want
