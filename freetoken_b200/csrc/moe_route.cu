@@ -13,21 +13,15 @@
 
 namespace ft {
 
-template <int WARPS>
-__global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
-                                     int* __restrict__ ids, float* __restrict__ weights, int T, int E,
-                                     int k, int softmax_scoring, int renormalize, float scale, int terms) {
-  extern __shared__ float smem[];  // [WARPS][2][E]: scores, choice values
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  pdl_wait();
-
-  const int t = blockIdx.x * WARPS + warp;
-  if (t >= T) return;
-  float* score = smem + (size_t)warp * 2 * E;
-  float* choice = score + E;
+// Scores and top-k of one token by one warp.  `score` and `choice` are E floats
+// of shared memory each.  With k <= 32 lane j < k returns the j-th choice in
+// (my_id, my_w); otherwise ids and weights go through `ids_out` / `weights_out`.
+__device__ __forceinline__ void select_token(const float* __restrict__ x, const float* __restrict__ bias,
+                                             float* score, float* choice, int* ids_out, float* weights_out,
+                                             int E, int k, int softmax_scoring, int renormalize, float scale,
+                                             int terms, int lane, int& my_id, float& my_w) {
   // a row holds `terms` partial logits per expert, E apart (the router weight
   // split into bfloat16 terms); they are summed in order, in float32
-  const float* x = logits + (size_t)t * E * terms;
   auto logit = [&](int e) {
     float v = x[e];
     for (int p = 1; p < terms; ++p) v += x[p * E + e];
@@ -55,8 +49,8 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   for (int e = lane; e < E; e += 32) choice[e] = score[e] + (bias ? bias[e] : 0.f);
   __syncwarp();
   float wsum = 0.f;
-  int my_id = 0;        // lane j keeps the j-th choice (k <= 32), else it goes through memory
-  float my_w = 0.f;
+  my_id = 0;            // lane j keeps the j-th choice (k <= 32), else it goes through memory
+  my_w = 0.f;
   for (int j = 0; j < k; ++j) {
     float best = -INFINITY;
     int arg = 0x7fffffff;
@@ -75,23 +69,120 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
     wsum += w;
     if (lane == (j & 31)) {
       if (k <= 32) { my_id = arg; my_w = w; }
-      else { ids[(size_t)t * k + j] = arg; weights[(size_t)t * k + j] = w; }
+      else { ids_out[j] = arg; weights_out[j] = w; }
     }
     if (lane == 0) choice[arg] = -INFINITY;
     __syncwarp();
   }
   if (k <= 32) {
-    if (lane < k) {
-      float w = my_w;
-      if (renormalize) w = w / (wsum + 1e-20f);
-      ids[(size_t)t * k + lane] = my_id;
-      weights[(size_t)t * k + lane] = w * scale;
-    }
+    if (renormalize) my_w = my_w / (wsum + 1e-20f);
+    my_w *= scale;
   } else if (lane == 0) {
     for (int j = 0; j < k; ++j) {
-      float w = weights[(size_t)t * k + j];
+      float w = weights_out[j];
       if (renormalize) w = w / (wsum + 1e-20f);
-      weights[(size_t)t * k + j] = w * scale;
+      weights_out[j] = w * scale;
+    }
+  }
+}
+
+template <int WARPS>
+__global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                     int* __restrict__ ids, float* __restrict__ weights, int T, int E,
+                                     int k, int softmax_scoring, int renormalize, float scale, int terms) {
+  extern __shared__ float smem[];  // [WARPS][2][E]: scores, choice values
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_wait();
+
+  const int t = blockIdx.x * WARPS + warp;
+  if (t >= T) return;
+  float* score = smem + (size_t)warp * 2 * E;
+  int my_id;
+  float my_w;
+  select_token(logits + (size_t)t * E * terms, bias, score, score + E, ids + (size_t)t * k,
+               weights + (size_t)t * k, E, k, softmax_scoring, renormalize, scale, terms, lane, my_id, my_w);
+  if (k <= 32 && lane < k) {
+    ids[(size_t)t * k + lane] = my_id;
+    weights[(size_t)t * k + lane] = my_w;
+  }
+}
+
+// A handful of tokens (a small decode batch): selection and the stable sort of
+// the few routes in ONE block and one launch.  Warp t selects for token t; then
+// a thread per expert counts its routes by walking the (at most 256) route ids
+// in shared memory, one warp scans the counts, and a thread per expert places
+// its routes in ascending order.  Same results as router_select + moe_sort.
+constexpr int SMALL_WARPS = 8;
+
+__global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
+    const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+    float* __restrict__ weights, int* __restrict__ counts, int* __restrict__ offsets,
+    int* __restrict__ sorted_route, int* __restrict__ sorted_token, int* __restrict__ active, int T, int E,
+    int k, int softmax_scoring, int renormalize, float scale, int terms) {
+  extern __shared__ float smem[];  // [T][2][E] scores and choices, then ints: ids [T*k], counts [E], before [E]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int R = T * k;
+  int* s_ids = reinterpret_cast<int*>(smem + (size_t)T * 2 * E);
+  int* s_cnt = s_ids + R;
+  int* s_before = s_cnt + E;
+  pdl_wait();
+
+  if (warp < T) {
+    int my_id;
+    float my_w;
+    float* score = smem + (size_t)warp * 2 * E;
+    select_token(logits + (size_t)warp * E * terms, bias, score, score + E, nullptr, nullptr, E, k,
+                 softmax_scoring, renormalize, scale, terms, lane, my_id, my_w);
+    if (lane < k) {
+      ids[warp * k + lane] = my_id;
+      weights[warp * k + lane] = my_w;
+      s_ids[warp * k + lane] = my_id;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int c = 0;
+    for (int r = 0; r < R; ++r) c += s_ids[r] == e;
+    s_cnt[e] = c;
+    counts[e] = c;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // exclusive scan over the experts: a lane takes a run of consecutive experts
+    const int per = (E + 31) / 32, begin = lane * per, end = min(E, begin + per);
+    int rows = 0, busy = 0;
+    for (int e = begin; e < end; ++e) { rows += s_cnt[e]; busy += s_cnt[e] > 0; }
+    int rows_before = rows, busy_before = busy;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, rows_before, o), b = __shfl_up_sync(0xffffffffu, busy_before, o);
+      if (lane >= o) { rows_before += a; busy_before += b; }
+    }
+    const int total_rows = __shfl_sync(0xffffffffu, rows_before, 31);
+    const int total_busy = __shfl_sync(0xffffffffu, busy_before, 31);
+    rows_before -= rows;
+    busy_before -= busy;
+    for (int e = begin; e < end; ++e) {
+      s_before[e] = rows_before;
+      offsets[e] = rows_before;
+      if (s_cnt[e] > 0) active[busy_before++] = e;
+      rows_before += s_cnt[e];
+    }
+    if (lane == 0) {
+      offsets[E] = total_rows;
+      active[E] = total_busy;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    if (s_cnt[e] == 0) continue;
+    int at = s_before[e];
+    for (int r = 0; r < R; ++r) {
+      if (s_ids[r] == e) {
+        sorted_route[at] = r;
+        sorted_token[at] = r / k;
+        ++at;
+      }
     }
   }
 }
@@ -370,6 +461,23 @@ int ft_router_select(const float* logits, const float* bias, int* ids, float* we
     cudaFuncSetAttribute(router_select_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   launch_pdl(router_select_kernel<WARPS>, dim3((T + WARPS - 1) / WARPS), dim3(WARPS * 32), smem, stream,
              logits, bias, ids, weights, T, E, k, softmax_scoring, renormalize, scale, terms);
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+// router_select + moe_sort in one launch; T <= 8 tokens, k <= 32.
+int ft_route_small(const float* logits, const float* bias, int* ids, float* weights, int* counts,
+                   int* offsets, int* sorted_route, int* sorted_token, int* active, int T, int E, int k,
+                   int softmax_scoring, int renormalize, float scale, int terms, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  if (T > SMALL_WARPS || k <= 0 || k > 32 || k > E || terms < 1) return FT_ERR_SHAPE;
+  const size_t smem = (size_t)T * 2 * E * sizeof(float) + ((size_t)T * k + 2 * (size_t)E) * sizeof(int);
+  if (smem > 160 * 1024) return FT_ERR_SHAPE;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(route_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  launch_pdl(route_small_kernel, dim3(1), dim3(SMALL_WARPS * 32), smem, stream, logits, bias, ids, weights,
+             counts, offsets, sorted_route, sorted_token, active, T, E, k, softmax_scoring, renormalize, scale,
+             terms);
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

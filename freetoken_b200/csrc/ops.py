@@ -640,6 +640,39 @@ def router_select(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch
              int(renormalize), float(scale), int(terms), _stream()), "router_select")
 
 
+ROUTE_SMALL_MAX_T = 8
+
+
+def route_small_takes(T: int, E: int, k: int) -> bool:
+    """A handful of tokens: selection and route sort fit one block."""
+    return T <= ROUTE_SMALL_MAX_T and k <= 32 and (T * 2 * E + T * k + 2 * E) * 4 <= 160 * 1024
+
+
+def route_small(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
+                weights: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor,
+                sorted_route: torch.Tensor, sorted_token: torch.Tensor, active: torch.Tensor, k: int,
+                softmax_scoring: bool, renormalize: bool, scale: float, terms: int = 1) -> None:
+    """:func:`router_select` and :func:`moe_sort` in one launch (same results)."""
+    _need(logits, "logits", torch.float32)
+    _need(weights, "weights", torch.float32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    for name, t in (("ids", ids), ("counts", counts), ("offsets", offsets),
+                    ("sorted_route", sorted_route), ("sorted_token", sorted_token), ("active", active)):
+        _need(t, name, torch.int32)
+    T, E = logits.shape[0], logits.shape[1] // terms
+    R = T * k
+    if logits.shape[1] != E * terms or not route_small_takes(T, E, k):
+        raise KernelError(f"route_small: refuses {T} tokens, {E} experts, top-{k}")
+    if counts.numel() < E or offsets.numel() < E + 1 or sorted_route.numel() < R \
+            or sorted_token.numel() < R or active.numel() < E + 1 or ids.numel() < R or weights.numel() < R:
+        raise KernelError("route_small: output buffers are too small")
+    f = _fn("moe_route", "ft_route_small", "p p p p p p p p p i i i i i f i")
+    _check(f(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(weights), _ptr(counts), _ptr(offsets),
+             _ptr(sorted_route), _ptr(sorted_token), _ptr(active), T, E, k, int(softmax_scoring),
+             int(renormalize), float(scale), int(terms), _stream()), "route_small")
+
+
 def router_logits_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.dtype == torch.float32)

@@ -116,8 +116,11 @@ class RoutedExperts(FeedForward):
         return libs + (["skinny_gemm", "moe_gemm_tc"] if dtype == torch.bfloat16 else [])
 
     # ---- forward ----------------------------------------------------------------
-    def route(self, ctx: StepContext, x: torch.Tensor):
-        """``(ids [T,k] int32, weights [T,k] float32)``."""
+    def route(self, ctx: StepContext, x: torch.Tensor, sort_into=None):
+        """``(ids [T,k] int32, weights [T,k] float32)``.  With ``sort_into``
+        (counts, offsets, sorted_route, sorted_token, active) the routes may be
+        sorted as well: returns ``(ids, weights, sorted?)``, the flag saying
+        whether that was done here (a handful of tokens: one launch for both)."""
         T = x.shape[0]
         ws = ctx.workspace
         logits = ws.get("moe.logits", (T, self.E), torch.float32)
@@ -135,25 +138,30 @@ class RoutedExperts(FeedForward):
             ops.gemm_rows(x, self.w_router, logits)
         ids = ws.get("moe.ids", (T, self.k), torch.int32)
         weights = ws.get("moe.weights", (T, self.k), torch.float32)
+        if sort_into is not None and ops.route_small_takes(T, self.E, self.k):
+            ops.route_small(logits, self.w_bias, ids, weights, *sort_into, self.k, self.softmax,
+                            self.renorm, self.scale, terms)
+            return ids, weights, True
         ops.router_select(logits, self.w_bias, ids, weights, self.k, self.softmax, self.renorm,
                           self.scale, terms)
-        return ids, weights
+        return (ids, weights) if sort_into is None else (ids, weights, False)
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
         R = T * self.k
         ws = ctx.workspace
-        ids, weights = self.route(ctx, x)
         counts = ws.get("moe.counts", (self.E,), torch.int32)
         offsets = ws.get("moe.offsets", (self.E + 1,), torch.int32)
         sorted_route = ws.get("moe.sorted_route", (R,), torch.int32)
         sorted_token = ws.get("moe.sorted_token", (R,), torch.int32)
         active = ws.get("moe.active", (self.E + 1,), torch.int32)
-        scratch = None
-        if R >= ops.MOE_SORT_CHUNKED_FROM:
-            scratch = ws.get("moe.sort_scratch", (ops.moe_sort_scratch(R, self.E),), torch.int32)
-        ops.moe_sort(ids.view(-1), counts, offsets, sorted_route, sorted_token, active, self.E, self.k,
-                     scratch)
+        ids, weights, is_sorted = self.route(ctx, x, (counts, offsets, sorted_route, sorted_token, active))
+        if not is_sorted:
+            scratch = None
+            if R >= ops.MOE_SORT_CHUNKED_FROM:
+                scratch = ws.get("moe.sort_scratch", (ops.moe_sort_scratch(R, self.E),), torch.int32)
+            ops.moe_sort(ids.view(-1), counts, offsets, sorted_route, sorted_token, active, self.E,
+                         self.k, scratch)
         if ctx.probe is not None:
             if "router_ids" in ctx.probe:
                 ctx.probe["router_ids"].append(ids.clone())

@@ -362,6 +362,36 @@ def test_router_select(E, k, softmax, renorm, use_bias, scale):
         assert ids[0].tolist() == list(range(k))
 
 
+@pytest.mark.parametrize("T,E,k,softmax,renorm,use_bias,scale,terms", [
+    (1, 256, 8, False, True, True, 2.0, 1), (8, 256, 8, False, True, True, 1.0, 1),
+    (7, 37, 5, True, False, False, 1.5, 1), (3, 5, 5, False, True, False, 0.5, 1),
+    (7, 600, 32, True, True, True, 1.0, 1), (8, 48, 4, False, True, True, 1.0, 3)])
+def test_route_small_equals_select_then_sort(T, E, k, softmax, renorm, use_bias, scale, terms):
+    """One launch for a handful of tokens: the same ids, weights, counts, offsets,
+    sorted routes and busy-expert list as router_select followed by moe_sort."""
+    o = ops()
+    logits = rnd(T, E * terms, seed=5)
+    logits[0, :] = 0.25
+    bias = rnd(E, seed=6, scale=0.1) if use_bias else None
+    R = T * k
+    i32 = lambda n, fill=-1: torch.full((n,), fill, dtype=torch.int32, device=DEV)
+
+    def buffers():
+        return dict(ids=i32(R).view(T, k), w=torch.zeros(T, k, device=DEV), counts=i32(E),
+                    offsets=i32(E + 1), sr=i32(R), st=i32(R), active=i32(E + 1))
+    a, b = buffers(), buffers()
+    o.router_select(logits, bias, a["ids"], a["w"], k, softmax, renorm, scale, terms)
+    o.moe_sort(a["ids"].view(-1), a["counts"], a["offsets"], a["sr"], a["st"], a["active"], E, k)
+    assert o.route_small_takes(T, E, k)
+    o.route_small(logits, bias, b["ids"], b["w"], b["counts"], b["offsets"], b["sr"], b["st"], b["active"],
+                  k, softmax, renorm, scale, terms)
+    busy = int(a["active"][E])
+    for name in ("ids", "counts", "offsets", "sr", "st"):
+        assert torch.equal(a[name], b[name]), name
+    assert torch.equal(a["w"], b["w"])
+    assert int(b["active"][E]) == busy and torch.equal(a["active"][:busy], b["active"][:busy])
+
+
 @pytest.mark.parametrize("T,E,H", [(70, 6, 128), (300, 256, 3072), (129, 37, 200)])
 def test_router_logits_from_bf16_terms(T, E, H):
     """The float32 router weight split into three bfloat16 terms: the terms sum
