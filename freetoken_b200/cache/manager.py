@@ -137,6 +137,9 @@ class CacheManager:
         # slots admitted since the last call of take_fresh_slots(): their
         # state rows have to be cleared on the device before they are used
         self._fresh: List[int] = []
+        # pages given back, kept for take_freed() when record_freed is set
+        self.record_freed = False
+        self._freed: List[Tuple[int, List[int]]] = []
 
     # ---- request slots --------------------------------------------------
     @property
@@ -227,9 +230,21 @@ class CacheManager:
             dead_below = max(0, new_len - w + 1) // self.page_size
             first = int(g.first_held[slot])
             if dead_below > first:
+                self._note_freed(g, g.block_table[slot, first:dead_below].tolist())
                 g.pool.release(g.block_table[slot, first:dead_below].tolist(), (request, id(g)))
                 g.block_table[slot, first:dead_below] = 0
                 g.first_held[slot] = dead_below
+
+    def _note_freed(self, group, pages: List[int]) -> None:
+        if self.record_freed and pages:
+            self._freed.append((self.paged_groups.index(group), list(pages)))
+
+    def take_freed(self) -> List[Tuple[int, List[int]]]:
+        """``(group index, pages)`` given back since the last call (only kept
+        when ``record_freed`` is set: a debugging aid that lets the engine
+        overwrite freed pages, so that a read of stale data shows)."""
+        out, self._freed = self._freed, []
+        return out
 
     def release(self, request: Hashable) -> None:
         """The request is over: pages and slot go back at once."""
@@ -237,6 +252,7 @@ class CacheManager:
         del self._request_of[slot]
         for g in self.paged_groups:
             first, filled = int(g.first_held[slot]), int(g.filled[slot])
+            self._note_freed(g, g.block_table[slot, first:filled].tolist())
             g.pool.release(g.block_table[slot, first:filled].tolist(), (request, id(g)))
             g.block_table[slot, :] = 0
             g.first_held[slot] = 0

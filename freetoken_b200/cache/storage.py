@@ -56,6 +56,15 @@ class CacheStorage:
         for t in self.state:
             t.index_fill_(1, index, 0)
 
+    def poison(self, group: int, pages: Sequence[int]) -> None:
+        """Overwrite pages (of every stop of a group, K and V) with NaN: a
+        debugging aid; a later read of a page's stale content then shows in the
+        logits instead of passing for data."""
+        if not pages:
+            return
+        index = torch.tensor(list(pages), dtype=torch.long, device=self.device)
+        self.paged[group].index_fill_(2, index, float("nan"))
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.paged + self.state)
 

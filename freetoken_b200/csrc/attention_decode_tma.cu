@@ -161,6 +161,18 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
     const unsigned char* tv = tk + NB * KB;
     const int j0 = k_begin + tile * TILE + warp * 16;    // first key of this warp's 16
     if (j0 <= pos && j0 + 15 >= first_valid) {
+      if (j0 + 15 > pos) {
+        // Keys past the request's last one: the box brought whatever the page held
+        // before.  Their scores are masked, but 0 * V must stay 0 even if an earlier
+        // request left a NaN or an infinity there: those V rows are zeroed.
+        unsigned char* vrows = const_cast<unsigned char*>(tv);
+        for (int idx = lane; idx < 16 * CH; idx += 32) {
+          const int r = idx / CH, c16 = idx % CH;
+          if (j0 + r > pos) *reinterpret_cast<uint4*>(vrows + sw_off(warp * 16 + r, c16)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async();
+        __syncwarp();
+      }
       float s[2][4];
 #pragma unroll
       for (int n = 0; n < 2; ++n)

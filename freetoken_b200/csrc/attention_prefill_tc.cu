@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
   unsigned char* sKr = sQ + Q_BYTES;                       // K ring [2]
   unsigned char* sVr = sKr + 2 * K_BYTES;                  // V ring [2]
   __shared__ __align__(8) unsigned long long q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2],
-      p_full[2], pv_done;
+      p_full[2], pv_done, v_clean;
   __shared__ unsigned tmem_slot;
   __shared__ volatile int gave_up;
 
@@ -94,6 +94,8 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
   const int tok0 = seg_begin + q0;
   const int pos_first = a.seg_pos0[seg] + q0;
   const int ntiles = (pos_first + rows - 1) / AK + 1;
+  // keys of the last tile past the segment's last token: whatever the page held before
+  const int stale_from = pos_first + rows - (ntiles - 1) * AK;      // first such key row, AK if none
 
   if (threadIdx.x == 0) {
     gave_up = 0;
@@ -104,6 +106,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4);
     }
     mbar_init(&pv_done, 1);
+    mbar_init(&v_clean, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -175,6 +178,31 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         }
       }
     }
+    // P is 0 at keys past the segment's end, but 0 * V must stay 0 even if an earlier
+    // request left a NaN or an infinity in the page: once the last V tile has landed
+    // this warp zeroes those rows (128 bytes per 64 head dims), then lets the O product go.
+    __syncwarp();
+    if (stale_from < AK && !gave_up) {
+      const int j = ntiles - 1;
+      bool ok = mbar_wait(&v_full[j & 1], ((unsigned)j >> 1) & 1u, &gave_up);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (ok) {
+        for (int idx = lane; idx < NB * AK; idx += 32) {
+          const int rr = idx % AK, hb = idx / AK;
+          if (rr >= stale_from) {
+            uint4* row = reinterpret_cast<uint4*>(sVr + (j & 1) * K_BYTES + hb * KB + rr * 128);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) row[c] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&v_clean);
+      } else if (lane == 0) {
+        atomicCAS(a.status, 0, 19);
+        gave_up = 1;
+      }
+    }
   } else if (warp == 1) {
     if (lane == 0) {
       // instruction descriptors: D f32, A/B bf16, M = 128; S: N = 64, both K-major;
@@ -211,7 +239,8 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         // held P of tile j-1, read by an O product issued before it (MMAs run in order)
         if (j + 1 < ntiles && !issue_s(j + 1)) break;
         if (!mbar_wait(&p_full[s], ((unsigned)j >> 1) & 1u, &gave_up) ||
-            !mbar_wait(&v_full[s], ((unsigned)j >> 1) & 1u, &gave_up)) {
+            !mbar_wait(&v_full[s], ((unsigned)j >> 1) & 1u, &gave_up) ||
+            (j == ntiles - 1 && stale_from < AK && !mbar_wait(&v_clean, 0, &gave_up))) {
           atomicCAS(a.status, 0, 14);
           gave_up = 1;
           break;

@@ -66,6 +66,7 @@ class EngineArgs:
     memory_ratio: float = 0.9
     max_step_tokens: int = 8192
     cuda_graph_max_bs: int = 64              # decode-only steps up to this batch are graph-replayed; 0: never
+    poison_freed_pages: bool = False         # debugging: pages given back are filled with NaN
 
 
 def _align4(n: int) -> int:
@@ -118,6 +119,12 @@ class Engine:
         self.max_seq_len = min(args.max_seq_len or max_pos, max_pos, num_pages * P)
         self.cache = CacheManager(needs, P, num_pages, args.max_running_requests, self.max_seq_len)
         self.storage = CacheStorage(self.cache, self.dtype, self.device)
+        if args.poison_freed_pages:
+            # every page but the sink starts out as unreadable as a freed one
+            self.cache.record_freed = True
+            for g, group in enumerate(self.cache.paged_groups):
+                first = group.pool.first_page
+                self.storage.poison(g, list(range(first, first + group.pool.num_pages)))
         self.workspace = Workspace(self.device)
         self.cache_views: List[CacheView] = []
         for i, stop in enumerate(self.plan.schedule):
@@ -167,6 +174,12 @@ class Engine:
         """The request is finished: what it holds is given back."""
         if self.cache.has_request(request):
             self.cache.release(request)
+            self._poison_freed()
+
+    def _poison_freed(self) -> None:
+        if self.args.poison_freed_pages:
+            for group, pages in self.cache.take_freed():
+                self.storage.poison(group, pages)
 
     def length(self, request: Hashable) -> int:
         return self.cache.length(request)
@@ -354,6 +367,7 @@ class Engine:
             self.model.forward(ctx, self.cache_views, logit_rows, logits, in_order)
         for e, seg in zip(entries, ctx.segments):
             self.cache.advance(e.request, seg.n)
+        self._poison_freed()        # pages a window has passed
         self.steps += 1
         self.tokens_run += ctx.num_tokens
         return logits

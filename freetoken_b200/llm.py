@@ -226,4 +226,6 @@ class LLM:
             if self.steps_since_check >= 64:
                 self.steps_since_check = 0
                 self.engine.check_status()
-        return self.scheduler.complete(step.plan, sampled)
+        done = self.scheduler.complete(step.plan, sampled)
+        self.engine._poison_freed()      # only in the page-poisoning debug mode
+        return done

@@ -41,6 +41,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
     p.add_argument("--max-running-requests", type=int, default=4,
                    help="most requests live at a time")
+    p.add_argument("--poison-freed-pages", action="store_true",
+                   help="debugging: fill cache pages with NaN whenever they are free, so that a read of "
+                        "stale data shows in the logits")
     return p
 
 
@@ -53,7 +56,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     pages = -(-args.max_tokens // page)
     engine = Engine.from_folder(args.model, EngineArgs(
         dtype=args.dtype, page_size=page, num_pages=pages,
-        max_running_requests=args.max_running_requests, max_seq_len=pages * page))
+        max_running_requests=args.max_running_requests, max_seq_len=pages * page,
+        poison_freed_pages=args.poison_freed_pages))
     import torch
 
     for line in sys.stdin:

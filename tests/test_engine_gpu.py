@@ -46,11 +46,11 @@ def requests_of(which):
     return {f"r{i}": tiny.tokens(100 * i + len(which), n, vocab) for i, n in enumerate(LENGTHS[which])}
 
 
-def make_engine(folder, dtype, page, max_tokens, live=4):
+def make_engine(folder, dtype, page, max_tokens, live=4, poison=False):
     from freetoken_b200.engine import Engine, EngineArgs
     return Engine.from_folder(folder, EngineArgs(dtype=dtype, page_size=page,
                                                  num_pages=-(-max_tokens // page),
-                                                 max_running_requests=live))
+                                                 max_running_requests=live, poison_freed_pages=poison))
 
 
 # In bfloat16 the discrete choice of experts may differ between two correct
@@ -135,6 +135,32 @@ def test_tcgen05_prefill_attention_in_the_engine(models, cut, monkeypatch):
     assert calls, "the tcgen05 attention kernel never ran"
     compare(got, plain_logits(models, which, dtype, reqs, routing), dtype, cut)
     assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+@pytest.mark.parametrize("which,dtype", [("A", "float32"), ("C", "bfloat16"), ("E", "bfloat16"), ("E", "float32")])
+def test_stale_pages_are_never_read(models, expected, which, dtype, monkeypatch):
+    """The mixed schedule again (pages reused while requests come and go), with
+    every free page filled with NaN: whenever it is free, a page is unreadable,
+    so any read of stale data - a masked key's V row times a zero weight
+    included - would turn logits into NaN.  tiny-E goes through the TMA-fed
+    attention kernels, which fetch whole 64-key boxes of a page."""
+    from freetoken_b200.csrc import ops
+    if which == "E":
+        monkeypatch.setattr(ops, "PREFILL_TC_MIN_SCORES", 0)
+    reqs = requests_of(which)
+    schedule = rd.mixed(reqs)
+    page = tiny.PAGE[which]
+    engine = make_engine(models[which], dtype, page, rd.peak_tokens(schedule, page), poison=True)
+    if dtype == "float32":
+        got = rd.run_engine(engine, reqs, schedule)
+        want = expected(which, dtype)
+    else:
+        routing = {}
+        got = rd.run_engine(engine, reqs, schedule, routing)
+        want = plain_logits(models, which, dtype, reqs, routing)
+    compare(got, want, dtype, "mixed, free pages poisoned")
+    pool = engine.storage.paged[0]
+    assert torch.isnan(pool[:, :, 1:].float()).all(), "a page that was given back is not poisoned"
 
 
 @pytest.mark.parametrize("which", ["A", "B"])
