@@ -188,14 +188,15 @@ def reference_unavailable() -> str:
     """Why the reference arm cannot run: tried against ``baseline/_ref``."""
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "freetoken")):
-        return ("the reference is not installed under baseline/_ref: pip cannot resolve its pinned "
-                "dependencies offline (apache-tvm-ffi==0.1.13.post3, flashlib==0.3.0 are not in the wheelhouse)")
+        return ("the reference is not installed under baseline/_ref (an offline install fails at its "
+                "pinned dependencies apache-tvm-ffi==0.1.13.post3 and flashlib==0.3.0, which no local "
+                "package source carries)")
     probe = subprocess.run([sys.executable, "-c", "import freetoken.llm"], capture_output=True, text=True,
                            env={**os.environ, "PYTHONPATH": ref})
     if probe.returncode != 0:
         last = (probe.stderr.strip().splitlines() or ["import failed"])[-1]
         return ("installed with --no-deps, but its public API does not import here: " + last +
-                " (flashlib is a hard dependency that is not in the wheelhouse)")
+                " (a hard dependency that is not installed)")
     return ("its MiniMax-M3 path serves NVFP4 experts through the expert offload cache only; there is "
             "no bfloat16 resident-weight configuration of this model to time")
 
@@ -383,7 +384,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     e2e_ms = timed(lambda: llm.run_step_overlapped(rngs), a.steps)
     llm.drain()
     h2d = engine.last_meta_ints * 4
-    d2h = a.batch * 4
+    d2h = llm.d2h_bytes_last_step      # the sampled tokens and the kernels' status word
     for r in list(llm.scheduler.running):
         llm.scheduler.abort(r.id)
 

@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
       for (int tile = 0; tile < ntiles; ++tile, ++issued) {
         const int s = tile % STAGES;
         if (!mbar_wait(&empty_bar[s], (((unsigned)(tile / STAGES)) & 1u) ^ 1u, &gave_up)) {
-          atomicCAS(a.status, 0, 21);
+          atomicCAS(a.status, 0, FT_ST_DECODE_PRODUCER);
           gave_up = 1;
           break;
         }
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
   for (int tile = 0; tile < ntiles; ++tile) {
     const int stage = tile % STAGES;
     bool ok = mbar_wait(&full_bar[stage], ((unsigned)(tile / STAGES)) & 1u, &gave_up);
-    if (!ok && lane == 0) { atomicCAS(a.status, 0, 22); gave_up = 1; }
+    if (!ok && lane == 0) { atomicCAS(a.status, 0, FT_ST_DECODE_CONSUMER); gave_up = 1; }
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) break;
     const unsigned char* tk = stages + stage * STAGE;

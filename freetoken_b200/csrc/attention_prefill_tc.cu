@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         if (j < ntiles) {
           const int s = j & 1;
           if (!mbar_wait(&k_empty[s], (((unsigned)j >> 1) & 1u) ^ 1u, &gave_up)) {
-            atomicCAS(a.status, 0, 11);
+            atomicCAS(a.status, 0, FT_ST_PREFILL_PRODUCER);
             gave_up = 1;
             break;
           }
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         if (j > 0) {
           const int i = j - 1, s = i & 1;
           if (!mbar_wait(&v_empty[s], (((unsigned)i >> 1) & 1u) ^ 1u, &gave_up)) {
-            atomicCAS(a.status, 0, 11);
+            atomicCAS(a.status, 0, FT_ST_PREFILL_PRODUCER);
             gave_up = 1;
             break;
           }
@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         __syncwarp();
         if (lane == 0) mbar_arrive(&v_clean);
       } else if (lane == 0) {
-        atomicCAS(a.status, 0, 19);
+        atomicCAS(a.status, 0, FT_ST_PREFILL_CLEANER);
         gave_up = 1;
       }
     }
@@ -212,13 +212,13 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(D >> 3) << 17) |
                                ((unsigned)(AQ >> 4) << 24);
       bool ok = mbar_wait(&q_full, 0, &gave_up);
-      if (!ok) { atomicCAS(a.status, 0, 12); gave_up = 1; }
+      if (!ok) { atomicCAS(a.status, 0, FT_ST_PREFILL_MMA_Q); gave_up = 1; }
       const unsigned sQa = smem_u32(sQ);
       // S product of tile j into S buffer j & 1; frees the K stage when done
       auto issue_s = [&](int j) -> bool {
         const int s = j & 1;
         if (!mbar_wait(&k_full[s], ((unsigned)j >> 1) & 1u, &gave_up)) {
-          atomicCAS(a.status, 0, 13);
+          atomicCAS(a.status, 0, FT_ST_PREFILL_MMA_K);
           gave_up = 1;
           return false;
         }
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         if (!mbar_wait(&p_full[s], ((unsigned)j >> 1) & 1u, &gave_up) ||
             !mbar_wait(&v_full[s], ((unsigned)j >> 1) & 1u, &gave_up) ||
             (j == ntiles - 1 && stale_from < AK && !mbar_wait(&v_clean, 0, &gave_up))) {
-          atomicCAS(a.status, 0, 14);
+          atomicCAS(a.status, 0, FT_ST_PREFILL_MMA_PV);
           gave_up = 1;
           break;
         }
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     for (int j = 0; j < ntiles; ++j) {
       const unsigned tmem_sj = tmem_s + (unsigned)((j & 1) * AK) + lane_bits;
       ok = mbar_wait(&s_full[j & 1], ((unsigned)j >> 1) & 1u, &gave_up);
-      if (!ok && lane == 0) { atomicCAS(a.status, 0, 15); gave_up = 1; }
+      if (!ok && lane == 0) { atomicCAS(a.status, 0, FT_ST_PREFILL_SOFTMAX_S); gave_up = 1; }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
@@ -301,7 +301,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         // O must be at rest: the previous tile's O product done (the one before it
         // is, since this tile's S product was issued after it), this tile's not issued
         ok = mbar_wait(&pv_done, (unsigned)(j - 1) & 1u, &gave_up);
-        if (!ok && lane == 0) { atomicCAS(a.status, 0, 16); gave_up = 1; }
+        if (!ok && lane == 0) { atomicCAS(a.status, 0, FT_ST_PREFILL_SOFTMAX_PV); gave_up = 1; }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         tc_fence_after();
@@ -341,13 +341,27 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       tc_st32(tmem_sj, pk);
       tc_st_wait();
       l += sum;
+      if (j == ntiles - 1 && j > 0) {
+        // A parity wait tells the phase it asks for from the one two earlier only
+        // while the waiter is at most one phase behind.  The wait after the loop asks
+        // for the O product of this last tile; this warp may have run ahead of its
+        // siblings (S of this tile was issued before the O product of tile j-1, which
+        // waits for all four warps and for V), so that product may not be done and the
+        // barrier would still be in phase j-1: the final wait would then be answered
+        // by phase j-2 and O read two products early.  Waiting here for product j-1,
+        // BEFORE this warp's arrival lets product j go, pins the phase.
+        ok = mbar_wait(&pv_done, (unsigned)(j - 1) & 1u, &gave_up);
+        if (!ok && lane == 0) { atomicCAS(a.status, 0, FT_ST_PREFILL_SOFTMAX_PV); gave_up = 1; }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[j & 1]);
     }
     if (ok) {
       ok = mbar_wait(&pv_done, (unsigned)(ntiles - 1) & 1u, &gave_up);
-      if (!ok && lane == 0) { atomicCAS(a.status, 0, 17); gave_up = 1; }
+      if (!ok && lane == 0) { atomicCAS(a.status, 0, FT_ST_PREFILL_SOFTMAX_LAST); gave_up = 1; }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     }
     if (ok) {

@@ -47,7 +47,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "moe_gemm_tc": "moe_gemm_tc.cu",
 }
-HEADERS: List[str] = ["common.cuh", "mma_utils.cuh", "tcgen05.cuh", "sampling_static.h"]
+HEADERS: List[str] = ["common.cuh", "mma_utils.cuh", "tcgen05.cuh", "status_codes.h", "sampling_static.h"]
 EXTRA_LINK: Dict[str, List[str]] = {}
 
 

@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
           const int s = (int)(issued % STAGES);
           const unsigned ph = (unsigned)(issued / STAGES) & 1u;
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, &gave_up)) {
-            atomicCAS(a.status, 0, 1);
+            atomicCAS(a.status, 0, FT_ST_MOE_PRODUCER);
             gave_up = 1;
             ok = false;
             break;
@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
                                ((unsigned)(TC_BM >> 4) << 24);
         const int b = local & 1;
         if (!mbar_wait(&acc_empty[b], ((unsigned)(local >> 1) & 1u) ^ 1u, &gave_up)) {
-          atomicCAS(a.status, 0, 4);
+          atomicCAS(a.status, 0, FT_ST_MOE_MMA_ACC);
           gave_up = 1;
           break;
         }
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
           const int s = (int)(done % STAGES);
           const unsigned ph = (unsigned)(done / STAGES) & 1u;
           if (!mbar_wait(&full_bar[s], ph, &gave_up)) {
-            atomicCAS(a.status, 0, 2);
+            atomicCAS(a.status, 0, FT_ST_MOE_MMA_STAGE);
             gave_up = 1;
             ok = false;
             break;
@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
         }
       }
       bool ok = mbar_wait(&acc_full[b], (unsigned)(local >> 1) & 1u, &gave_up);
-      if (!ok && lane == 0) { atomicCAS(a.status, 0, 3); gave_up = 1; }
+      if (!ok && lane == 0) { atomicCAS(a.status, 0, FT_ST_MOE_EPILOGUE); gave_up = 1; }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       tc_fence_after();
@@ -338,6 +338,26 @@ __global__ void moe_tile_map_kernel(const int* __restrict__ group_offsets, const
   for (int i = carry + threadIdx.x; i < bound; i += blockDim.x) tile_expert[i] = -1;
 }
 
+// Exercises the bounded wait itself: thread 0 waits (at most `limit_ns`) on an
+// mbarrier that thread 1 arrives at only when `arrive` is set.  When the wait
+// runs out the thread records its code in the status word, as every role of the
+// kernels above does, and the kernel returns normally.
+__global__ void wait_selftest_kernel(int* status, unsigned long long limit_ns, int arrive) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ volatile int gave_up;
+  if (threadIdx.x == 0) {
+    gave_up = 0;
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 1 && arrive) mbar_arrive(&bar);
+  if (threadIdx.x == 0 && !mbar_wait(&bar, 0, &gave_up, limit_ns)) {
+    atomicCAS(status, 0, FT_ST_SELFTEST_WAIT);
+    gave_up = 1;
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -388,6 +408,16 @@ int ft_tc_make_map(void* out, const void* base, long long groups, long long rows
   }
   if (rc != CUDA_SUCCESS) return -202;
   memcpy(out, &map, sizeof(map));
+  return FT_OK;
+}
+
+// One block whose first thread waits up to `limit_ns` nanoseconds (at most a
+// second) on a barrier that is arrived at only if `arrive` is non-zero; a wait
+// that runs out leaves FT_ST_SELFTEST_WAIT in `status`.
+int ft_wait_selftest(int* status, long long limit_ns, int arrive, cudaStream_t stream) {
+  if (!status || limit_ns < 0 || limit_ns > 1000000000ll) return FT_ERR_SHAPE;
+  wait_selftest_kernel<<<1, 32, 0, stream>>>(status, (unsigned long long)limit_ns, arrive);
+  FT_LAUNCH_CHECK();
   return FT_OK;
 }
 

@@ -301,20 +301,49 @@ def tc_status(device) -> torch.Tensor:
     return _TC_STATUS[idx]
 
 
+def _status_table() -> Dict[int, tuple]:
+    """``{code: (kernel, role)}`` read from the ``X(name, code, "kernel", "role")``
+    lines of ``status_codes.h``, the header the kernels take the numbers from."""
+    global _STATUS_TABLE
+    if _STATUS_TABLE is None:
+        import re
+        text = open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "status_codes.h")).read()
+        _STATUS_TABLE = {int(c): (kernel, role) for _, c, kernel, role in
+                         re.findall(r'X\((\w+),\s*(\d+),\s*"([^"]+)",\s*"([^"]+)"\)', text)}
+    return _STATUS_TABLE
+
+
+_STATUS_TABLE: Optional[Dict[int, tuple]] = None
+
+
+def status_message(code_: int) -> str:
+    kernel, role = _status_table().get(int(code_), ("a kernel", "a role"))
+    return f"{kernel}: {role} waited on a barrier beyond its limit and gave up (code {int(code_)})"
+
+
+def raise_for_status(code_: int, device) -> None:
+    """Turn a status code that was read from the device into a :class:`KernelError`
+    and clear the device word, so that the next check reports new failures only."""
+    if code_:
+        tc_status(device).zero_()
+        raise KernelError(status_message(code_))
+
+
 def check_tc_status(device) -> None:
-    """Raise if a tensor-core kernel gave up a wait since the last check (synchronises)."""
+    """Raise if a kernel gave up a bounded wait since the last check (synchronises)."""
     idx = torch.device(device).index or 0
     if idx in _TC_STATUS:
-        code_ = int(_TC_STATUS[idx].item())
-        if code_:
-            _TC_STATUS[idx].zero_()
-            kernel = "attn_prefill_tc" if code_ > 10 else "moe_gemm_tc"
-            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "the MMA issuer",
-                    11: "the TMA producer", 12: "the MMA issuer", 13: "the MMA issuer",
-                    14: "the MMA issuer", 15: "the softmax warps", 16: "the softmax warps",
-                    17: "the softmax warps"}.get(code_, "a role")
-            raise KernelError(f"{kernel}: {role} waited on a barrier for over two seconds and gave up "
-                              f"(code {code_})")
+        raise_for_status(int(_TC_STATUS[idx].item()), device)
+
+
+def wait_selftest(device, limit_ns: int, arrive: bool) -> None:
+    """Launch one block whose first thread waits up to ``limit_ns`` on a barrier
+    that is arrived at only if ``arrive``: the bounded wait every tcgen05 / TMA
+    kernel here uses, made to run out on purpose (nothing hangs: the wait ends
+    by its own limit and the kernel returns)."""
+    f = _fn("moe_gemm_tc", "ft_wait_selftest", "p q i")
+    with torch.cuda.device(torch.device(device)):
+        _check(f(_ptr(tc_status(device)), int(limit_ns), int(bool(arrive)), _stream()), "wait_selftest")
 
 
 def _tc_map(t: torch.Tensor, rows: int, K: int, row_stride: int, groups: int, box_rows: int):
@@ -396,6 +425,31 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
              _ptr(c_rows), _ptr(row_scale),
              _ptr(status), rows, N, K, G, ntok, int(glu), 0 if act == "silu" else 1,
              float(act_alpha), float(act_limit), _stream()), "moe_gemm_tc")
+
+
+def moe_experts_tc(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, mid: torch.Tensor,
+                   parts: torch.Tensor, group_offsets: torch.Tensor, active: torch.Tensor,
+                   sorted_route: torch.Tensor, sorted_token: torch.Tensor, route_weight: torch.Tensor,
+                   rows: int, act: str, act_alpha: float, act_limit: float, workspace) -> None:
+    """Both expert products of a step on the tcgen05 grouped GEMM:
+    ``mid[sorted row] = act(Wgate x) * (Wup x)`` over the routes sorted by expert,
+    then ``parts[route] = route_weight[route] * (Wdown mid)``.  ``x`` is ``[T, H]``,
+    ``sorted_token`` / ``sorted_route`` give the token and the route of every sorted
+    row, ``group_offsets`` / ``active`` come from :func:`moe_sort`."""
+    G = w_gate_up.shape[0]
+    xs = workspace.get("moe.sorted_x", (rows, x.shape[1]), x.dtype)
+    gather_rows(x, sorted_token, xs)
+    ntok = tc_tokens_per_tile(rows, G)
+    tiles = moe_tile_map(group_offsets, active, rows, G, ntok, workspace)
+    moe_gemm_tc(xs, w_gate_up, mid, group_offsets=group_offsets, active=active, tile_map=tiles,
+                rows=rows, glu=True, act=act, act_alpha=act_alpha, act_limit=act_limit,
+                tokens_per_tile=ntok)
+    # the down projection takes wider token tiles when experts are busy enough
+    ntok2 = tc_tokens_per_tile(rows, G, wide=True)
+    if ntok2 != ntok:
+        tiles = moe_tile_map(group_offsets, active, rows, G, ntok2, workspace, tag=".wide")
+    moe_gemm_tc(mid, w_down, parts, group_offsets=group_offsets, active=active, tile_map=tiles,
+                c_rows=sorted_route, row_scale=route_weight, rows=rows, tokens_per_tile=ntok2)
 
 
 def pass_rows(rows: int) -> int:

@@ -5,6 +5,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "status_codes.h"
 
 namespace ft {
 
@@ -32,16 +33,21 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false after ~2 s or once another role has given up.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* gave_up) {
+// Bounded wait: false after `limit_ns` (about two seconds unless the caller says
+// otherwise), after a fixed number of polls whatever the clock says, or once
+// another role has given up.
+constexpr unsigned long long FT_WAIT_LIMIT_NS = 2000000000ull;
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* gave_up,
+                                          unsigned long long limit_ns = FT_WAIT_LIMIT_NS) {
   if (mbar_try(bar, parity)) return true;
   const unsigned long long start = global_ns();
-  for (;;) {
+  for (long long round = 0; round < (1ll << 28); ++round) {
     for (int i = 0; i < 64; ++i)
       if (mbar_try(bar, parity)) return true;
     if (*gave_up) return false;
-    if (global_ns() - start > 2000000000ull) return false;
+    if (global_ns() - start > limit_ns) return false;
   }
+  return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
                                             unsigned long long* bar) {

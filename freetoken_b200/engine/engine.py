@@ -29,6 +29,7 @@ from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage, kv_bytes_per_token
 from ..csrc import build, ops
 from ..models.model import Model
+from ..parts import linear
 from ..parts.base import PREFILL_TILE, CacheView, Segment, StepContext, Workspace
 from ..registry import Architecture, architecture_of, get_architecture, read_model_config
 from ..weights.loader import check_state, load_tensors
@@ -91,6 +92,9 @@ class Engine:
         self.plan = arch.build_plan(config)
         self.model = Model(self.plan)
         build.ensure_built(self.model.libraries(self.dtype))
+        if self.dtype == torch.bfloat16:
+            # asked once, here, so that no step (or graph capture) has to find out
+            linear.library_offers_f32_out(self.device)
         specs = self.model.tensor_specs()
         if tensors is None and folder is not None:
             tensors = load_tensors(specs, folder, self.dtype, self.device, arch.rename_tensor,

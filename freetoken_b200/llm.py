@@ -18,6 +18,7 @@ from typing import Any, Dict, List, Optional, Sequence, Union
 
 import torch
 
+from .csrc import ops
 from .engine.engine import Engine, EngineArgs, StepEntry
 from .engine.scheduler import PlannedEntry, Request, Scheduler
 from .sampling.params import SamplingParams
@@ -54,6 +55,7 @@ class _InFlight:
         self.index_of = index_of            # request id -> place among the sampled tokens
         self.tokens_dev: Optional[torch.Tensor] = None
         self.tokens_host: Optional[torch.Tensor] = None
+        self.status_host: Optional[torch.Tensor] = None     # the kernels' status word after this step
         self.event: Optional[torch.cuda.Event] = None
 
 
@@ -99,7 +101,8 @@ class LLM:
         self._flip = 0
         self._tok_dev: List[Optional[torch.Tensor]] = [None, None]
         self._tok_host: List[Optional[torch.Tensor]] = [None, None]
-        self.steps_since_check = 0
+        self._status_host = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.d2h_bytes_last_step = 0
 
     # ---- text ------------------------------------------------------------
     def _tokenizer(self):
@@ -145,8 +148,12 @@ class LLM:
         results = []
         for r in requests:
             out = list(r.output)
-            if r.finish_reason == "stop" and out and not r.params.ignore_eos:
-                out = out[:-1]      # the EOS token itself is not part of the answer (llm.py:101-103)
+            if (r.finish_reason == "stop" and out and not r.params.ignore_eos
+                    and out[-1] in self.eos_token_ids):
+                # the EOS token itself is not part of the answer; a token that ended the
+                # request through stop_token_ids or a stop string is
+                # (python/freetoken/llm/llm.py:101-103)
+                out = out[:-1]
             text = self.tokenizer.decode(out) if self.tokenizer is not None else ""
             results.append({"text": text, "token_ids": out, "finish_reason": r.finish_reason})
         return results
@@ -209,6 +216,12 @@ class LLM:
             step.tokens_dev = self.sampler.sample(logits, params, uniforms, out=self._tok_dev[k])
             step.tokens_host = self._tok_host[k]
             step.tokens_host[:len(samplers)].copy_(step.tokens_dev, non_blocking=True)
+            # the word in which a kernel records a wait that ran out travels with the
+            # tokens, so a failed step is noticed before its tokens are used (the
+            # reference checks after every step too: engine/engine.py:922-925)
+            step.status_host = self._status_host[k]
+            step.status_host.copy_(ops.tc_status(self.engine.device), non_blocking=True)
+            self.d2h_bytes_last_step = 4 * len(samplers) + 4
             step.event = torch.cuda.Event()
             step.event.record()
         return step
@@ -221,11 +234,8 @@ class LLM:
         sampled: List[int] = []
         if step.count:
             step.event.synchronize()
+            ops.raise_for_status(int(step.status_host[0]), self.engine.device)
             sampled = step.tokens_host[:step.count].tolist()
-            self.steps_since_check += 1
-            if self.steps_since_check >= 64:
-                self.steps_since_check = 0
-                self.engine.check_status()
         done = self.scheduler.complete(step.plan, sampled)
         self.engine._poison_freed()      # only in the page-poisoning debug mode
         return done

@@ -7,8 +7,11 @@
   ``torch.matmul``), as the reference does for its dense projections
   (python/freetoken/layers/linear.py:31-32).  Few rows (decode) go through the
   weight-streaming kernel of ``skinny_gemm.cu`` instead.
-* bfloat16 compute, float32 result (logits, router logits): our kernels, so the
-  result leaves the float32 accumulator unrounded.
+* bfloat16 compute, float32 result (logits of many rows, the router's logits
+  of a long step): the library product with a float32 result where this
+  PyTorch offers one (``torch.mm(..., out_dtype=float32)``), else the
+  weight-streaming kernel; either way the result is the float32 accumulator,
+  never a rounded bfloat16.
 """
 
 from __future__ import annotations
@@ -43,19 +46,28 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Te
 _F32_OUT = {"ok": None}
 
 
+def library_offers_f32_out(device) -> bool:
+    """Whether ``torch.mm`` takes ``out_dtype`` (asked once, on a tiny product).
+    Only "this PyTorch has no such argument" counts as no; any other error is
+    a real one and is raised."""
+    if _F32_OUT["ok"] is None:
+        a = torch.zeros((16, 16), dtype=torch.bfloat16, device=device)
+        try:
+            torch.mm(a, a.t(), out_dtype=torch.float32)
+            _F32_OUT["ok"] = True
+        except (TypeError, NotImplementedError):
+            _F32_OUT["ok"] = False
+    return _F32_OUT["ok"]
+
+
 def library_f32_out(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
     """bfloat16 x bfloat16 -> float32 through the library product, where this
-    PyTorch offers it (``torch.mm(..., out_dtype=)``); the result is the
-    float32 accumulator, not a rounded bfloat16."""
-    if _F32_OUT["ok"] is False:
+    PyTorch offers it; the result is the float32 accumulator, not a rounded
+    bfloat16.  False: the caller takes one of our kernels instead."""
+    if not library_offers_f32_out(x.device):
         return False
-    try:
-        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
-        _F32_OUT["ok"] = True
-        return True
-    except (TypeError, RuntimeError):
-        _F32_OUT["ok"] = False
-        return False
+    torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+    return True
 
 
 # Up to this many rows the weight-streaming kernel reads the weights once;

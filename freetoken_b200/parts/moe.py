@@ -107,7 +107,10 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor], dtype) -> None:
         self.w_router = tensors[self.n_router]
         self.w_router_terms = bf16_terms(self.w_router) if dtype == torch.bfloat16 else None
-        self.w_bias = tensors.get(self.n_bias) if self.use_bias else None
+        # The bias is part of the routing whenever the checkpoint carries it: the
+        # reference's block always adds it (python/freetoken/models/minimax_m3/moe.py:75,
+        # weight.py:220).  ``use_bias`` only decides whether its absence is an error.
+        self.w_bias = tensors.get(self.n_bias)
         self.w_gate_up = tensors[self.n_gate_up]
         self.w_down = tensors[self.n_down]
 
@@ -179,21 +182,10 @@ class RoutedExperts(FeedForward):
         if ctx.dtype == torch.bfloat16 and R > TC_MIN_ROWS_PER_EXPERT * self.E \
                 and ops.moe_gemm_tc_takes(x, self.w_gate_up, mid) \
                 and ops.moe_gemm_tc_takes(mid, self.w_down, parts):
-            # many rows per expert: tcgen05 grouped GEMM over the gathered rows
-            xs = ctx.workspace.get("moe.sorted_x", (R, self.hidden), ctx.dtype)
-            ops.gather_rows(x, sorted_token, xs)
-            ntok = ops.tc_tokens_per_tile(R, self.E)
-            tiles = ops.moe_tile_map(offsets, active, R, self.E, ntok, ctx.workspace)
-            ops.moe_gemm_tc(xs, self.w_gate_up, mid, group_offsets=offsets, active=active,
-                            tile_map=tiles, rows=R, glu=True, act=self.act, act_alpha=self.act_alpha,
-                            act_limit=self.act_limit, tokens_per_tile=ntok)
-            # the down projection takes wider token tiles when experts are busy enough
-            ntok2 = ops.tc_tokens_per_tile(R, self.E, wide=True)
-            if ntok2 != ntok:
-                tiles = ops.moe_tile_map(offsets, active, R, self.E, ntok2, ctx.workspace, tag=".wide")
-            ops.moe_gemm_tc(mid, self.w_down, parts, group_offsets=offsets, active=active,
-                            tile_map=tiles, c_rows=sorted_route, row_scale=route_weight, rows=R,
-                            tokens_per_tile=ntok2)
+            # many rows per expert: tcgen05 grouped GEMM over the rows sorted by expert
+            ops.moe_experts_tc(x, self.w_gate_up, self.w_down, mid, parts, offsets, active, sorted_route,
+                               sorted_token, route_weight, R, self.act, self.act_alpha, self.act_limit,
+                               ctx.workspace)
             return
         if ctx.dtype == torch.bfloat16 and ops.skinny_gemm_takes(x, self.w_gate_up, mid) \
                 and ops.skinny_gemm_takes(mid, self.w_down, parts):

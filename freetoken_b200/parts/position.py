@@ -11,11 +11,31 @@ engine can reach.  ``none`` rotates nothing.
 
 from __future__ import annotations
 
-from typing import Optional
+from typing import Dict, Optional, Tuple
 
 import torch
 
 from .base import Position, register_position
+
+# One cos|sin table per (rotary_dim, theta, device), shared by every layer that
+# rotates the same way (the reference shares one module through a cached
+# ``get_rope``, python/freetoken/layers/rotary.py:212-213).  A table only grows.
+_TABLES: Dict[Tuple[int, float, torch.device], torch.Tensor] = {}
+
+
+def rotary_table(rotary_dim: int, theta: float, device, positions: int) -> torch.Tensor:
+    """``[>= positions, rotary_dim]`` float32 on ``device``: ``cos | sin`` of
+    ``position * theta^(-2i/rotary_dim)``, computed on the host in float32."""
+    key = (int(rotary_dim), float(theta), torch.device(device))
+    table = _TABLES.get(key)
+    if table is None or table.shape[0] < positions:
+        r = int(rotary_dim)
+        inv_freq = 1.0 / (float(theta) ** (torch.arange(0, r, 2, dtype=torch.float) / r))
+        t = torch.arange(positions, dtype=torch.float)
+        freqs = torch.einsum("i,j -> ij", t, inv_freq)
+        table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(device)
+        _TABLES[key] = table
+    return table
 
 
 class _Rotary(Position):
@@ -29,20 +49,13 @@ class _Rotary(Position):
         self.max_position = int(spec.params["max_position"])
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and within head_dim {self.head_dim}")
-        self._table: Optional[torch.Tensor] = None
 
     def table(self, device, positions: int) -> Optional[torch.Tensor]:
-        """``[positions, rotary_dim]`` float32 on ``device`` (``None`` when nothing rotates)."""
+        """``[>= positions, rotary_dim]`` float32 on ``device`` (``None`` when
+        nothing rotates); every layer with the same rotation gets the same tensor."""
         if self.rotary_dim == 0:
             return None
-        positions = min(positions, self.max_position)
-        if self._table is None or self._table.shape[0] < positions or self._table.device != torch.device(device):
-            r = self.rotary_dim
-            inv_freq = 1.0 / (self.theta ** (torch.arange(0, r, 2, dtype=torch.float) / r))
-            t = torch.arange(positions, dtype=torch.float)
-            freqs = torch.einsum("i,j -> ij", t, inv_freq)
-            self._table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).contiguous().to(device)
-        return self._table
+        return rotary_table(self.rotary_dim, self.theta, device, min(positions, self.max_position))
 
 
 @register_position("rotary_neox")

@@ -39,6 +39,12 @@ class Sampler:
         self.vocab_size = vocab_size
         self._probs: Optional[torch.Tensor] = None
         self._out: Optional[torch.Tensor] = None
+        # per-row options travel through two pinned buffers taken in turn; a buffer
+        # is written again only after the copy that last read it has finished
+        self._pinned: List[Optional[torch.Tensor]] = [None, None]
+        self._pinned_done: List[Optional[torch.cuda.Event]] = [None, None]
+        self._options_dev: Optional[torch.Tensor] = None
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                uniforms: Sequence[float], out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -55,16 +61,31 @@ class Sampler:
             ops.sample(logits, None, None, None, None, out, None)
             return out
         V = logits.shape[1]
-        host = np.zeros((4, rows), dtype=np.float32)
+        turn = self._turn
+        self._turn ^= 1
+        cap = 0 if self._options_dev is None else self._options_dev.shape[1]
+        if cap < rows:
+            # larger batch than before: new buffers on both sides, [4, cap] each
+            cap = max(rows, 64)
+            torch.cuda.current_stream().synchronize()
+            self._options_dev = torch.empty((4, cap), dtype=torch.float32, device=self.device)
+            self._pinned = [torch.zeros((4, cap), dtype=torch.float32).pin_memory() for _ in range(2)]
+            self._pinned_done = [torch.cuda.Event() for _ in range(2)]
+        else:
+            self._pinned_done[turn].synchronize()
+        host = self._pinned[turn].numpy()
         for i, p in enumerate(params):
             host[0, i] = 0.0 if p.is_greedy else max(p.temperature, MIN_T)
             host[1, i] = min(max(p.top_p, MIN_P), 1.0)
             host[2, i] = min(max(uniforms[i], 0.0), 0.99999994)
         ks = np.asarray([p.top_k if 1 <= p.top_k < V else 0 for p in params], dtype=np.int32)
-        host[3, :] = ks.view(np.float32)
-        dev = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
+        host[3, :rows] = ks.view(np.float32)
+        dev = self._options_dev
+        dev.copy_(self._pinned[turn], non_blocking=True)
+        self._pinned_done[turn].record()
         if self._probs is None or self._probs.numel() < rows * V:
             self._probs = torch.empty(rows * V, dtype=torch.float32, device=self.device)
-        ops.sample(logits, dev[0], dev[3].view(torch.int32) if ks.any() else None,
-                   dev[1] if (host[1] < 1.0).any() else None, dev[2], out, self._probs)
+        ops.sample(logits, dev[0, :rows], dev[3, :rows].view(torch.int32) if ks.any() else None,
+                   dev[1, :rows] if (host[1, :rows] < 1.0).any() else None, dev[2, :rows], out,
+                   self._probs)
         return out

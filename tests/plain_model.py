@@ -273,7 +273,9 @@ class PlainModel:
         residual = residual + a
         h2 = self.rnd(rms_norm(residual, self.w(f"{p}.post_attention_layernorm.weight"), self.eps, self.plus_one))
         m = f"{p}.block_sparse_moe"
-        bias = self.tensors[f"{m}.e_score_correction_bias"] if self.use_bias else None
+        # the block adds the bias whenever the checkpoint has it: minimax_m3/moe.py:75, weight.py:220
+        bias = self.tensors[f"{m}.e_score_correction_bias"] if self.use_bias \
+            else self.tensors.get(f"{m}.e_score_correction_bias")
         wts, ids = route(h2, self.tensors[f"{m}.gate.weight"], bias, self.k, self.scoring,
                          self.renorm, self.route_scale, forced_ids, self.routing)
         gate_up = [torch.cat([self.w(f"{m}.experts.{e}.w1.weight"), self.w(f"{m}.experts.{e}.w3.weight")])

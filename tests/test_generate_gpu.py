@@ -5,6 +5,7 @@ import pytest
 import torch
 
 import tiny
+from generation_check import check_generation
 from plain_model import PlainModel
 
 pytestmark = pytest.mark.gpu
@@ -18,6 +19,55 @@ def folder_a(tmp_path_factory):
 @pytest.fixture(scope="module")
 def folder_c(tmp_path_factory):
     return tiny.write_tiny(str(tmp_path_factory.mktemp("genC")), "C")
+
+
+@pytest.fixture(scope="module")
+def folder_b(tmp_path_factory):
+    return tiny.write_tiny(str(tmp_path_factory.mktemp("genB")), "B")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tiny_b_workload_against_a_plain_sampling_loop(folder_b, dtype):
+    """tiny-B (tied head, softmax routing, 3 KV heads of 24): four requests with
+    prompts of 1/6/13/31 tokens in portions of at most 7, temperature 0.8 at seed 3,
+    6 new tokens each, pages of 8.  The test draws the same uniform numbers from the
+    request's generator and requires the tokens of a plain softmax(logits/T) +
+    inverse-CDF loop over the plain model."""
+    from freetoken_b200 import LLM, SamplingParams
+    from freetoken_b200.sampling.sampler import RequestRng
+    vocab = tiny.TINY_B["vocab_size"]
+    prompts = [tiny.tokens(s, n, vocab) for s, n in ((1, 1), (2, 6), (3, 13), (4, 31))]
+    params = SamplingParams(temperature=0.8, max_tokens=6, ignore_eos=True, seed=3)
+    llm = LLM(folder_b, dtype, page_size=8, num_token_override=160, max_running_req=4,
+              max_extend_tokens=7)
+    out = llm.generate(prompts, params)
+    plain = PlainModel(folder_b, dtype)
+    ties = 0
+    for prompt, result in zip(prompts, out):
+        rng = RequestRng(3)
+        uniforms = [rng.next_uniform() for _ in range(6)]
+        assert len(result["token_ids"]) == 6
+        ties += check_generation(plain, prompt, result["token_ids"], dtype, 0.8, uniforms)
+    # a vocabulary of 384 near-uniform tokens puts a boundary within about 1e-3 of most
+    # draws, so bfloat16 may land next door often; float32 may not at all
+    assert dtype == "bfloat16" or ties == 0, f"{ties} of 24 tokens were decided by a tie"
+    llm.scheduler.check_integrity()
+    assert llm.engine.cache.free_pages() == llm.engine.cache.total_pages()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["B", "C"])
+def test_greedy_generation_against_the_plain_model(folder_b, folder_c, which, dtype):
+    from freetoken_b200 import LLM, SamplingParams
+    folder = {"B": folder_b, "C": folder_c}[which]
+    vocab = tiny.TINY[which]["vocab_size"]
+    prompts = [tiny.tokens(s, n, vocab) for s, n in ((5, 3), (6, 11), (7, 26))]
+    llm = LLM(folder, dtype, page_size=tiny.PAGE[which], num_token_override=192, max_running_req=3,
+              max_extend_tokens=9)
+    out = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    plain = PlainModel(folder, dtype)
+    ties = sum(check_generation(plain, p, r["token_ids"], dtype) for p, r in zip(prompts, out))
+    assert ties == 0 if dtype == "float32" else ties < 12, f"{ties} of 24 tokens were decided by a tie"
 
 
 def test_greedy_generation_float32(folder_a):
@@ -105,7 +155,14 @@ def test_eos_stops_generation(folder_a):
     stop_at = free[3]
     if stop_at in free[:3]:
         pytest.skip("the chosen stop token appears earlier")
+    # a stop token that is no EOS ends the request and stays in the answer
+    # (python/freetoken/llm/llm.py:101-103 drops EOS ids only)
     out = llm.generate([prompt], SamplingParams(max_tokens=8, stop_token_ids=[stop_at]))[0]
+    assert out["token_ids"] == free[:4] and out["finish_reason"] == "stop"
+    # the same token as the model's EOS: dropped
+    llm.eos_token_ids = [stop_at]
+    llm.scheduler.eos = {stop_at}
+    out = llm.generate([prompt], SamplingParams(max_tokens=8))[0]
     assert out["token_ids"] == free[:3] and out["finish_reason"] == "stop"
 
 

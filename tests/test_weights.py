@@ -150,3 +150,33 @@ def test_random_mode_is_seeded_per_tensor(tmp_path):
     na = read_safetensors(str(tmp_path / "A" / "model.safetensors"))
     assert torch.all(na["model.norm.weight"].float() == 1.0)
     assert float(na["model.layers.0.block_sparse_moe.e_score_correction_bias"].std()) > 0
+
+
+def test_a_score_correction_bias_in_the_checkpoint_is_used_even_if_the_config_is_silent(tmp_path):
+    """The reference's block always adds ``e_score_correction_bias`` when it chooses
+    experts (python/freetoken/models/minimax_m3/moe.py:75) and its loader always
+    reads it (weight.py:220): a config.json without ``use_routing_bias`` must not
+    make routing ignore a bias the checkpoint carries."""
+    with_bias = dict(tiny.TINY_B, use_routing_bias=True)
+    folder = tiny.write_tiny(str(tmp_path), "B", config=with_bias)
+    silent = {k: v for k, v in tiny.TINY_B.items() if k != "use_routing_bias"}
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(silent, f)
+    arch = architecture_of(silent)
+    model = Model(arch.build_plan(arch.read_config(silent)))
+    tensors = load_tensors(model.tensor_specs(), folder, torch.float32, "cpu", arch.rename_tensor)
+    name = "model.layers.1.block_sparse_moe.e_score_correction_bias"
+    assert name in tensors and tensors[name].dtype == torch.float32
+    model.bind(tensors, torch.float32)
+    for block in model.blocks:
+        assert block.feed_forward.w_bias is not None
+    # absent and not asked for: fine, and no bias is used
+    folder2 = tiny.write_tiny(str(tmp_path / "plain"), "B")
+    tensors = load_tensors(model.tensor_specs(), folder2, torch.float32, "cpu", arch.rename_tensor)
+    model.bind(tensors, torch.float32)
+    assert all(block.feed_forward.w_bias is None for block in model.blocks)
+    # asked for and absent: one error that names it
+    model = Model(arch.build_plan(arch.read_config(with_bias)))
+    with pytest.raises(WeightError) as err:
+        load_tensors(model.tensor_specs(), folder2, torch.float32, "cpu", arch.rename_tensor)
+    assert name in err.value.missing
