@@ -34,19 +34,62 @@ import numpy as np
 from .pages import OutOfPages, PageAccountingError, PagePool
 
 
+class PerTokenNeed:
+    """Base of needs that keep something for every token of a request, in
+    pages.  A need states the layout of its pages and what a token costs; the
+    manager pools stops with equal needs, the storage allocates
+    ``[stops, *layout(pages, page_size)]`` per group.  ``window`` = how many
+    latest tokens are still read (``None``: all of them): pages the window has
+    passed are given back while the request runs.  ``storage_dtype`` names the
+    element type (``None``: the engine's activation dtype).
+
+    A cache of another shape per token (one latent vector instead of keys and
+    values, keys and values of different widths) is another subclass; nothing in
+    the manager, the storage or the engine names a particular one."""
+
+    kind = "per_token"
+    window: Optional[int] = None
+    storage_dtype: Optional[str] = None
+    page_axis = 0            # which axis of ``layout`` counts pages
+
+    def layout(self, pages: int, page_size: int) -> Tuple[int, ...]:
+        raise NotImplementedError
+
+    def elements_per_token(self) -> int:
+        raise NotImplementedError
+
+
+class PerRequestNeed:
+    """Base of needs that keep a tensor of fixed ``shape`` per request, carried
+    from step to step in the request's slot and cleared when it is admitted."""
+
+    kind = "per_request"
+    shape: Tuple[int, ...] = ()
+    dtype: str = "float32"
+
+
 @dataclass(frozen=True)
-class PagedKVNeed:
+class PagedKVNeed(PerTokenNeed):
     """Keys and values per token; ``window`` = how many latest keys are read
-    (``None``: all of them)."""
+    (``None``: all of them).  Pages are ``[2 (K, V), pages, kv_heads, page_size,
+    head_dim]``: a page of one KV head is ``page_size * head_dim`` contiguous
+    elements, the tile the attention kernels stream."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     kind: str = "paged_kv"
+    page_axis = 1
+
+    def layout(self, pages: int, page_size: int) -> Tuple[int, ...]:
+        return (2, pages, self.num_kv_heads, page_size, self.head_dim)
+
+    def elements_per_token(self) -> int:
+        return 2 * self.num_kv_heads * self.head_dim
 
 
 @dataclass(frozen=True)
-class StateNeed:
+class StateNeed(PerRequestNeed):
     """A tensor of fixed ``shape`` per request, carried from step to step."""
 
     shape: Tuple[int, ...]
@@ -54,14 +97,14 @@ class StateNeed:
     kind: str = "state"
 
 
-CacheNeed = PagedKVNeed | StateNeed
+CacheNeed = PerTokenNeed | PerRequestNeed
 
 
 @dataclass
 class PageGroup:
     """Stops with the same paged need: own pool, own block table."""
 
-    need: PagedKVNeed
+    need: PerTokenNeed
     stops: List[int]
     pool: PagePool
     block_table: np.ndarray  # int32 [max_slots, max_pages_per_request], 0 = sink page
@@ -73,7 +116,7 @@ class PageGroup:
 
 @dataclass
 class StateGroup:
-    need: StateNeed
+    need: PerRequestNeed
     stops: List[int]
 
 
@@ -101,11 +144,11 @@ class CacheManager:
         # stop -> (group index, index of the stop inside the group)
         self.paged_index: Dict[int, Tuple[int, int]] = {}
         self.state_index: Dict[int, Tuple[int, int]] = {}
-        paged_needs: List[PagedKVNeed] = []
+        paged_needs: List[PerTokenNeed] = []
         for stop, need in enumerate(needs):
             if need is None:
                 continue
-            if need.kind == "paged_kv":
+            if isinstance(need, PerTokenNeed):
                 if need not in paged_needs:
                     paged_needs.append(need)
                     g = len(paged_needs) - 1
@@ -119,7 +162,7 @@ class CacheManager:
                 g = paged_needs.index(need)
                 self.paged_index[stop] = (g, len(self.paged_groups[g].stops))
                 self.paged_groups[g].stops.append(stop)
-            elif need.kind == "state":
+            elif isinstance(need, PerRequestNeed):
                 for g, group in enumerate(self.state_groups):
                     if group.need == need:
                         break
@@ -129,7 +172,8 @@ class CacheManager:
                 self.state_index[stop] = (g, len(self.state_groups[g].stops))
                 self.state_groups[g].stops.append(stop)
             else:
-                raise ValueError(f"stop {stop}: unknown cache need {need!r}")
+                raise ValueError(f"stop {stop}: a cache need is a PerTokenNeed or a PerRequestNeed, "
+                                 f"not {need!r}")
         self._free_slots: List[int] = list(range(max_slots - 1, -1, -1))
         self._slot_of: Dict[Hashable, int] = {}
         self._request_of: Dict[int, Hashable] = {}

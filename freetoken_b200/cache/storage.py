@@ -1,6 +1,7 @@
 """Device memory behind the cache manager.
 
-One tensor per page group, ``[stops, 2 (K,V), pages, kv_heads, page_size,
+One tensor per page group, ``[stops, *need.layout(pages, page_size)]``; for
+keys and values that is ``[stops, 2 (K,V), pages, kv_heads, page_size,
 head_dim]``: a page of one KV head is ``page_size * head_dim`` contiguous
 elements, which is the tile attention kernels stream.  (The reference's pool is
 ``[2, layers, pages, page_size, kv_heads, head_dim]``,
@@ -29,9 +30,9 @@ class CacheStorage:
         self.paged: List[torch.Tensor] = []
         for g in manager.paged_groups:
             pages = g.pool.first_page + g.pool.num_pages
-            self.paged.append(torch.zeros(
-                (len(g.stops), 2, pages, g.need.num_kv_heads, manager.page_size, g.need.head_dim),
-                dtype=kv_dtype, device=self.device))
+            dtype = kv_dtype if g.need.storage_dtype is None else _STATE_DTYPES[g.need.storage_dtype]
+            self.paged.append(torch.zeros((len(g.stops),) + tuple(g.need.layout(pages, manager.page_size)),
+                                          dtype=dtype, device=self.device))
         self.state: List[torch.Tensor] = []
         for g in manager.state_groups:
             self.state.append(torch.zeros(
@@ -39,7 +40,8 @@ class CacheStorage:
                 dtype=_STATE_DTYPES[g.need.dtype], device=self.device))
 
     def kv_of_stop(self, stop: int) -> torch.Tensor:
-        """``[2, pages, kv_heads, page_size, head_dim]`` of one cache-owning stop."""
+        """The pages of one cache-owning stop in its need's layout (keys and
+        values: ``[2, pages, kv_heads, page_size, head_dim]``)."""
         g, i = self.manager.paged_index[stop]
         return self.paged[g][i]
 
@@ -57,24 +59,26 @@ class CacheStorage:
             t.index_fill_(1, index, 0)
 
     def poison(self, group: int, pages: Sequence[int]) -> None:
-        """Overwrite pages (of every stop of a group, K and V) with NaN: a
+        """Overwrite pages (of every stop of a group, all they hold) with NaN: a
         debugging aid; a later read of a page's stale content then shows in the
         logits instead of passing for data."""
         if not pages:
             return
         index = torch.tensor(list(pages), dtype=torch.long, device=self.device)
-        self.paged[group].index_fill_(2, index, float("nan"))
+        axis = 1 + self.manager.paged_groups[group].need.page_axis
+        self.paged[group].index_fill_(axis, index, float("nan"))
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.paged + self.state)
 
 
 def kv_bytes_per_token(manager_needs, kv_dtype: torch.dtype) -> int:
-    """Bytes one token costs over all paged stops (sizing the pool from free
-    memory, cf. python/freetoken/kvcache/mha_pool.py:85-94)."""
-    size = torch.empty((), dtype=kv_dtype).element_size()
+    """Bytes one token costs over all stops that keep something per token
+    (sizing the pool from free memory, cf. python/freetoken/kvcache/mha_pool.py:85-94)."""
+    from .manager import PerTokenNeed
     total = 0
     for need in manager_needs:
-        if need is not None and need.kind == "paged_kv":
-            total += 2 * need.num_kv_heads * need.head_dim * size
+        if isinstance(need, PerTokenNeed):
+            dtype = kv_dtype if need.storage_dtype is None else _STATE_DTYPES[need.storage_dtype]
+            total += need.elements_per_token() * torch.empty((), dtype=dtype).element_size()
     return total

@@ -34,15 +34,34 @@ class LayerSpec:
     """The parts of one decoder layer and the block that arranges them.
 
     ``prefix`` is the tensor-name prefix of the layer's weights
-    (``model.layers.3``); every part reads its tensors below it.
+    (``model.layers.3``); every part reads its tensors below it.  The block kind
+    decides what a layer consists of: which norms it has (by the names the block
+    knows them under) and whether it has a feed-forward at all.  The usual two
+    norms have fields of their own (``mixer_norm`` is the norm named ``"mixer"``,
+    ``feed_forward_norm`` the one named ``"feed_forward"``); any further norm of
+    a block with more of them (post-norms, a sandwich) goes into ``norms``.
     """
 
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward: Optional[PartSpec] = None
+    mixer_norm: Optional[PartSpec] = None
+    feed_forward_norm: Optional[PartSpec] = None
+    norms: Mapping[str, PartSpec] = field(default_factory=dict)
+
+    def all_norms(self) -> Dict[str, PartSpec]:
+        """Every norm of the layer by name."""
+        out: Dict[str, PartSpec] = {}
+        if self.mixer_norm is not None:
+            out["mixer"] = self.mixer_norm
+        if self.feed_forward_norm is not None:
+            out["feed_forward"] = self.feed_forward_norm
+        for name, spec in self.norms.items():
+            if name in out:
+                raise ValueError(f"layer '{self.prefix}': the norm '{name}' is given twice")
+            out[name] = spec
+        return out
 
 
 @dataclass(frozen=True)

@@ -30,7 +30,7 @@ from ..cache.storage import CacheStorage, kv_bytes_per_token
 from ..csrc import build, ops
 from ..models.model import Model
 from ..parts import linear
-from ..parts.base import PREFILL_TILE, CacheView, Segment, StepContext, Workspace
+from ..parts.base import CacheView, Segment, StepContext, StepShape, Workspace
 from ..registry import Architecture, architecture_of, get_architecture, read_model_config
 from ..weights.loader import check_state, load_tensors
 from ..weights.random_init import RandomOptions, random_state
@@ -130,6 +130,9 @@ class Engine:
                 first = group.pool.first_page
                 self.storage.poison(g, list(range(first, first + group.pool.num_pages)))
         self.workspace = Workspace(self.device)
+        # parts whose kernels want step metadata of their own, one per plan key
+        self._planners = self.model.step_planners()
+        self._graphs_allowed = self.model.graph_capturable()
         self.cache_views: List[CacheView] = []
         for i, stop in enumerate(self.plan.schedule):
             owner = self.plan.cache_owner(i)
@@ -267,20 +270,22 @@ class Engine:
             width = min(-(-width // 8) * 8, self.cache.max_pages_per_request)
         groups = self.cache.paged_groups
 
+        # what the parts plan for their own kernels (row lists, tile lists)
+        shape = StepShape(segments, T, P, width, max_q, max_kv)
+        plans = {key: part.plan_step(shape) for key, part in self._planners.items()}
+
         # packed layout, every section 16-byte aligned
         off = {}
         cur = 0
-        dec_rows = [s.q_start for s in segments if s.n == 1]
-        pre_rows = [r for s in segments if s.n > 1 for r in range(s.q_start, s.q_start + s.n)]
-        pf_tiles = [(i, q0) for i, s in enumerate(segments) if s.n > 1
-                    for q0 in range(0, s.n, PREFILL_TILE)]
         for name, size in (("token_ids", T), ("token_pos", T), ("token_seg", T), ("seg_slot", S),
                            ("seg_pos0", S), ("seg_q_start", S + 1), ("seg_kv_len", S),
-                           ("logit_rows", N), ("dec_rows", len(dec_rows)),
-                           ("pre_rows", len(pre_rows)), ("pf_tile_seg", len(pf_tiles)),
-                           ("pf_tile_q0", len(pf_tiles))):
+                           ("logit_rows", N)):
             off[name] = cur
             cur = _align4(cur + size)
+        for i, plan in enumerate(plans.values()):
+            for name, array in plan.arrays.items():
+                off[f"plan{i}.{name}"] = cur
+                cur = _align4(cur + int(array.size))
         for g in range(len(groups)):
             off[f"table{g}"] = cur
             cur = _align4(cur + S * width)
@@ -309,15 +314,10 @@ class Engine:
         h[off["seg_q_start"] + S] = T
         if N:
             h[off["logit_rows"]: off["logit_rows"] + N] = np.asarray(rows, dtype=np.int32)
-        mixed = bool(dec_rows) and bool(pre_rows)
-        if dec_rows:
-            h[off["dec_rows"]: off["dec_rows"] + len(dec_rows)] = np.asarray(dec_rows, dtype=np.int32)
-        if pre_rows:
-            h[off["pre_rows"]: off["pre_rows"] + len(pre_rows)] = np.asarray(pre_rows, dtype=np.int32)
-        if pf_tiles:
-            tiles = np.asarray(pf_tiles, dtype=np.int32)
-            h[off["pf_tile_seg"]: off["pf_tile_seg"] + len(pf_tiles)] = tiles[:, 0]
-            h[off["pf_tile_q0"]: off["pf_tile_q0"] + len(pf_tiles)] = tiles[:, 1]
+        for i, plan in enumerate(plans.values()):
+            for name, array in plan.arrays.items():
+                if array.size:
+                    h[off[f"plan{i}.{name}"]: off[f"plan{i}.{name}"] + array.size] = array
         if patches:
             pp = np.asarray(patches, dtype=np.int32)
             h[off["patch_rows"]: off["patch_rows"] + len(patches)] = pp[:, 0]
@@ -334,6 +334,8 @@ class Engine:
             ops.patch_tokens(sec("token_ids", T), sec("patch_rows", len(patches)), token_source,
                              sec("patch_src", len(patches)), vocab)
 
+        for i, plan in enumerate(plans.values()):
+            plan.tensors = {name: sec(f"plan{i}.{name}", int(array.size)) for name, array in plan.arrays.items()}
         ctx = StepContext(
             device=self.device, dtype=self.dtype, segments=segments, num_tokens=T,
             token_ids=sec("token_ids", T), token_pos=sec("token_pos", T),
@@ -341,15 +343,7 @@ class Engine:
             seg_q_start=sec("seg_q_start", S + 1), seg_kv_len=sec("seg_kv_len", S),
             block_tables=[sec(f"table{g}", S * width).view(S, width) for g in range(len(groups))],
             workspace=self.workspace, page_size=P, max_q_len=max_q, max_kv_len=max_kv,
-            max_positions=self.max_seq_len,
-            decode_rows=sec("dec_rows", len(dec_rows)) if mixed else None,
-            prefill_rows=sec("pre_rows", len(pre_rows)) if mixed else None,
-            num_decode_rows=len(dec_rows), num_prefill_rows=len(pre_rows),
-            prefill_tile_seg=sec("pf_tile_seg", len(pf_tiles)),
-            prefill_tile_q0=sec("pf_tile_q0", len(pf_tiles)), num_prefill_tiles=len(pf_tiles),
-            prefill_scores=sum(s.n * (s.pos0 + (s.n + 1) // 2) for s in segments if s.n > 1),
-            max_decode_kv_len=(width * P if max_q == 1 else
-                               max((s.pos0 + 1 for s in segments if s.n == 1), default=0)))
+            max_positions=self.max_seq_len, plans=plans)
         in_order = N == T and rows == list(range(T))
         return ctx, sec("logit_rows", N), N, in_order
 
@@ -385,7 +379,7 @@ class Engine:
         T = ctx.num_tokens
         if (probe is not None or not ctx.decode_only or not in_order or N != T
                 or T > self.args.cuda_graph_max_bs or self.dtype != torch.bfloat16
-                or self.cache.state_groups):
+                or not self._graphs_allowed):
             return False
         key = (T, tuple(t.shape[1] for t in ctx.block_tables), self.workspace.generation,
                self._meta_generation)

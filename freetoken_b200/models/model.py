@@ -9,14 +9,14 @@ its :class:`CacheView`.
 
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
 from ..cache.manager import CacheNeed
 from ..config.model_plan import ModelPlan, PartSpec
 from ..csrc import ops
-from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Block, CacheView,
+from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Block, CacheView, Part,
                           StepContext)
 from ..weights.spec import TensorSpec
 
@@ -32,11 +32,16 @@ class Model:
         self.embedding = EMBEDDINGS.get(plan.embedding.kind)(plan.embedding, _prefix(plan.embedding, ""))
         self.blocks: List[Block] = []
         for layer in plan.layers:
+            # the layer's spec lists what it has; the block kind says what it needs
+            block_cls = BLOCKS.get(layer.block.kind)
+            norm_specs = layer.all_norms()
+            block_cls.check_parts(layer.prefix, sorted(norm_specs), layer.feed_forward is not None)
             mixer = MIXERS.get(layer.mixer.kind)(layer.mixer, layer.prefix)
-            ffn = FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward, layer.prefix)
-            n1 = NORMS.get(layer.mixer_norm.kind)(layer.mixer_norm, layer.prefix)
-            n2 = NORMS.get(layer.feed_forward_norm.kind)(layer.feed_forward_norm, layer.prefix)
-            self.blocks.append(BLOCKS.get(layer.block.kind)(layer.block, layer.prefix, mixer, ffn, n1, n2))
+            ffn = None
+            if layer.feed_forward is not None:
+                ffn = FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward, layer.prefix)
+            norms = {name: NORMS.get(spec.kind)(spec, layer.prefix) for name, spec in norm_specs.items()}
+            self.blocks.append(block_cls(layer.block, layer.prefix, mixer, ffn, norms))
         self.final_norm = NORMS.get(plan.final_norm.kind)(plan.final_norm, _prefix(plan.final_norm, ""))
         self.head = HEADS.get(plan.head.kind)(plan.head, _prefix(plan.head, ""))
 
@@ -66,6 +71,33 @@ class Model:
                 if lib not in names:
                     names.append(lib)
         return names
+
+    def leaf_parts(self) -> List[Part]:
+        """Every part of the model, the parts inside blocks (and inside those) included."""
+        out: List[Part] = []
+
+        def walk(part: Part) -> None:
+            out.append(part)
+            for child in part.children():
+                walk(child)
+        for part in self.parts():
+            walk(part)
+        return out
+
+    def step_planners(self) -> Dict[Hashable, Part]:
+        """One part per distinct ``step_plan_key``: the parts whose kernels want
+        step metadata of their own (parts with equal keys share one plan)."""
+        planners: Dict[Hashable, Part] = {}
+        for part in self.leaf_parts():
+            key = part.step_plan_key()
+            if key is not None and key not in planners:
+                planners[key] = part
+        return planners
+
+    def graph_capturable(self) -> bool:
+        """Whether every part says that its forward pass may be recorded into a CUDA
+        graph and replayed with new step metadata at the same addresses."""
+        return all(part.graph_capturable for part in self.leaf_parts())
 
     # ---- cache -------------------------------------------------------------
     def cache_needs(self) -> List[Optional[CacheNeed]]:

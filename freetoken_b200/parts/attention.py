@@ -18,13 +18,17 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 
 from ..cache.manager import PagedKVNeed
 from ..csrc import ops
 from ..weights.spec import Cat, Init, Name, TensorSpec
 from . import linear
-from .base import POSITIONS, CacheView, Mixer, StepContext, register_mixer
+from .base import POSITIONS, CacheView, Mixer, StepContext, StepPlan, StepShape, register_mixer
+
+# query tokens per tile of the prefill attention kernels' tile list
+PREFILL_TILE = 64
 
 _NORM_MODES = {"none": 0, "per_layer": 1, "per_head": 2}
 
@@ -36,6 +40,8 @@ class PagedAttention(Mixer):
     sliding_window`` (None: all keys), ``position`` (a PartSpec), ``scope`` and
     ``checkpoint_names`` (q, k, v, o, fused qkv, q_norm, k_norm tensor names
     below the scope)."""
+
+    graph_capturable = True
 
     def __init__(self, spec, prefix):
         super().__init__(spec, prefix)
@@ -64,6 +70,43 @@ class PagedAttention(Mixer):
         self.n_knorm = f"{self.scope}.{names['k_norm']}"
         self._split = [f"{self.scope}.{names[k]}" for k in ("q", "k", "v")]
         self.w_qkv = self.w_o = self.w_qnorm = self.w_knorm = None
+
+    def children(self):
+        return [self.position]
+
+    # ---- step metadata ---------------------------------------------------------
+    def step_plan_key(self):
+        # the lists depend on the step's segments only: every attention layer shares them
+        return "paged_attention"
+
+    def plan_step(self, shape: StepShape) -> StepPlan:
+        """What the attention kernels want to know about a step: which token rows
+        are single-token segments (decode kernel; listed only when the step also
+        has longer segments, otherwise it is all rows), the 64-token query tiles
+        of the longer segments (prefill kernels: segment and first token inside
+        it), how many query-key pairs those score, and the longest context of a
+        decode row (in whole block-table rows for a decode-only step, so that the
+        split count - and with it a captured graph - stays put while contexts grow)."""
+        segs = shape.segments
+        dec = [s.q_start for s in segs if s.n == 1]
+        tiles = [(i, q0) for i, s in enumerate(segs) if s.n > 1 for q0 in range(0, s.n, PREFILL_TILE)]
+        arrays = {
+            "tile_seg": np.asarray([t[0] for t in tiles], dtype=np.int32),
+            "tile_q0": np.asarray([t[1] for t in tiles], dtype=np.int32),
+        }
+        if dec and tiles:
+            arrays["decode_rows"] = np.asarray(dec, dtype=np.int32)
+        if shape.max_q_len == 1:
+            max_decode_kv = shape.table_width * shape.page_size
+        else:
+            max_decode_kv = max((s.pos0 + 1 for s in segs if s.n == 1), default=0)
+        host = {
+            "num_decode_rows": len(dec),
+            "num_prefill_tiles": len(tiles),
+            "prefill_scores": sum(s.n * (s.pos0 + (s.n + 1) // 2) for s in segs if s.n > 1),
+            "max_decode_kv_len": max_decode_kv,
+        }
+        return StepPlan(arrays=arrays, host=host)
 
     # ---- cache and weights ------------------------------------------------
     def cache_need(self):
@@ -120,24 +163,24 @@ class PagedAttention(Mixer):
 
     def attend(self, ctx: StepContext, q, o, cache: CacheView, table) -> None:
         """Single-token rows go to the split-KV tensor-core kernel, rows of
-        longer segments to the prefill kernel; sizes those refuse (and the
-        float32 path) go to the generic kernel.  ``decode_rows`` /
-        ``prefill_rows`` are only set when a step has both kinds."""
+        longer segments to a prefill kernel; sizes those refuse (and the
+        float32 path) go to the generic kernel."""
         if ops.attn_decode_takes(q, self.d):
-            if ctx.num_decode_rows > 0:
-                ops.attn_decode(q, o, cache.kv_pages, ctx.decode_rows, ctx.num_decode_rows,
+            plan = ctx.plan(self)
+            n_dec, n_tiles = plan.host["num_decode_rows"], plan.host["num_prefill_tiles"]
+            if n_dec > 0:
+                ops.attn_decode(q, o, cache.kv_pages, plan.tensors.get("decode_rows"), n_dec,
                                 ctx.token_pos, ctx.token_seg, table, self.nq, self.nkv, self.d,
-                                self.scale, self.window, ctx.max_decode_kv_len, ctx.workspace)
-            if ctx.num_prefill_tiles > 0:
-                if (ctx.prefill_scores >= ops.PREFILL_TC_MIN_SCORES
+                                self.scale, self.window, plan.host["max_decode_kv_len"], ctx.workspace)
+            if n_tiles > 0:
+                tile_seg, tile_q0 = plan.tensors["tile_seg"], plan.tensors["tile_q0"]
+                if (plan.host["prefill_scores"] >= ops.PREFILL_TC_MIN_SCORES
                         and ops.attn_prefill_tc_takes(q, cache.kv_pages, self.d, self.window)):
-                    ops.attn_prefill_tc(q, o, cache.kv_pages, ctx.prefill_tile_seg, ctx.prefill_tile_q0,
-                                        ctx.seg_q_start, ctx.seg_pos0, table, self.nq, self.nkv, self.d,
-                                        self.scale)
+                    ops.attn_prefill_tc(q, o, cache.kv_pages, tile_seg, tile_q0, ctx.seg_q_start,
+                                        ctx.seg_pos0, table, self.nq, self.nkv, self.d, self.scale)
                     return
-                ops.attn_prefill(q, o, cache.kv_pages, ctx.prefill_tile_seg, ctx.prefill_tile_q0,
-                                 ctx.seg_q_start, ctx.seg_pos0, table, self.nq, self.nkv, self.d,
-                                 self.scale, self.window)
+                ops.attn_prefill(q, o, cache.kv_pages, tile_seg, tile_q0, ctx.seg_q_start, ctx.seg_pos0,
+                                 table, self.nq, self.nkv, self.d, self.scale, self.window)
             return
         ops.attn_paged_simt(q, o, cache.kv_pages, ctx.token_pos, ctx.token_seg, table,
                             self.nq, self.nkv, self.d, self.scale, self.window)

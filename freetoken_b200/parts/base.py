@@ -10,14 +10,21 @@ Kinds of parts and what each must offer:
 * **Norm**          ``forward(ctx, delta, residual) -> normed``.  Adds ``delta``
   (``[T, H]``, ``[T, k, H]`` or ``None``) into the float32 ``residual`` in place
   and returns the normalised rows in the activation dtype.
-* **Position**      tables or constants a mixer applies to queries and keys.
+* **Position**      what a mixer applies to queries and keys: ``rotary_dim``,
+  ``interleaved`` and ``table(device, positions)`` (``cos | sin`` per position).
 * **Mixer**         ``cache_need()`` says what the cache manager must keep for
-  it (paged keys/values, a fixed-size state, or nothing);
+  it (pages of per-token data, a fixed-size state, or nothing);
   ``forward(ctx, x, cache) -> y`` mixes the tokens of each request in order.
 * **FeedForward**   ``forward(ctx, x) -> y``, token by token.  ``y`` is ``[T, H]``
   or ``[T, k, H]``: k partial rows per token that the next norm adds in order.
-* **Block**         arranges a mixer, a feed-forward and their norms around the
-  residual stream: ``forward(ctx, delta, residual, cache) -> delta``.
+* **Block**         arranges a mixer, a feed-forward (if it has one) and the
+  norms it names around the residual stream:
+  ``forward(ctx, delta, residual, cache) -> delta``.
+
+Any part whose kernels want step metadata of their own (row lists, tile lists)
+states a ``step_plan_key()`` and builds the lists in ``plan_step(shape)``; the
+engine packs them into the step's one metadata copy and the part finds them
+under ``ctx.plan(self)``.
 * **Embedding / Head**  token ids -> residual rows; normed rows -> logits.
 
 The reference wires the same roles by attribute walks over ``BaseOP`` objects
@@ -28,8 +35,9 @@ python/freetoken/core.py:112-207); here the context is an argument.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Callable, Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheNeed
@@ -80,7 +88,28 @@ class Workspace:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 
 
-PREFILL_TILE = 64   # query tokens per tile of the prefill attention kernel
+@dataclass
+class StepShape:
+    """The host-side facts of a step a part may plan from."""
+
+    segments: List[Segment]
+    num_tokens: int
+    page_size: int
+    table_width: int       # entries of a block-table row in this step
+    max_q_len: int
+    max_kv_len: int
+
+
+@dataclass
+class StepPlan:
+    """Step metadata of one part (or of all parts with the same plan key):
+    ``arrays`` are int32 lists that travel to the device with the step's metadata
+    (afterwards found in ``tensors`` under the same names), ``host`` holds counts
+    and sizes the part reads when it chooses and launches its kernels."""
+
+    arrays: Dict[str, np.ndarray] = field(default_factory=dict)
+    host: Dict[str, Any] = field(default_factory=dict)
+    tensors: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
 @dataclass
@@ -106,20 +135,9 @@ class StepContext:
     max_q_len: int = 1
     max_kv_len: int = 1
     max_positions: int = 0             # longest sequence the engine can hold
-    # token rows of single-token segments (decode) and of longer segments, as
-    # device int32 tensors; None when the step has none of that kind
-    decode_rows: Optional[torch.Tensor] = None
-    prefill_rows: Optional[torch.Tensor] = None
-    num_decode_rows: int = 0
-    num_prefill_rows: int = 0
-    max_decode_kv_len: int = 0
-    # query tiles (PREFILL_TILE tokens) of the longer segments: segment index
-    # and first token inside the segment, device int32
-    prefill_tile_seg: Optional[torch.Tensor] = None
-    prefill_tile_q0: Optional[torch.Tensor] = None
-    num_prefill_tiles: int = 0
-    # query-key pairs the longer segments score (n * (pos0 + n/2), summed)
-    prefill_scores: int = 0
+    # step metadata of the parts that plan their own, by plan key (the engine
+    # fills this; a context made by hand gets a part's plan at its first use)
+    plans: Dict[Hashable, StepPlan] = field(default_factory=dict)
     # when set, parts may leave measurements here (the benchmark counts the
     # experts a step touched); never set on the serving path
     probe: Optional[Dict[str, Any]] = None
@@ -132,24 +150,64 @@ class StepContext:
     def decode_only(self) -> bool:
         return self.max_q_len == 1
 
+    def shape(self) -> StepShape:
+        width = self.block_tables[0].shape[1] if self.block_tables else 0
+        return StepShape(self.segments, self.num_tokens, self.page_size, width, self.max_q_len,
+                         self.max_kv_len)
+
+    def plan(self, part: "Part") -> StepPlan:
+        """The step metadata ``part`` planned.  The engine has it ready; for a
+        context built by hand it is planned and copied to the device here."""
+        key = part.step_plan_key()
+        plan = self.plans.get(key)
+        if plan is None:
+            plan = part.plan_step(self.shape())
+            for name, array in plan.arrays.items():
+                plan.tensors[name] = torch.from_numpy(np.ascontiguousarray(array, dtype=np.int32)).to(self.device)
+            self.plans[key] = plan
+        return plan
+
 
 @dataclass
 class CacheView:
     """What one stop of the schedule sees of the cache."""
 
-    kv_pages: Optional[torch.Tensor] = None     # [2, pages, kv_heads, page, head_dim]
+    # the stop's pages in the layout its need states (keys and values:
+    # [2, pages, kv_heads, page, head_dim])
+    kv_pages: Optional[torch.Tensor] = None
     block_table_index: int = 0                   # which entry of ctx.block_tables
     state: Optional[torch.Tensor] = None         # [slots + 1, *shape]
     writes: bool = True                          # False: reads another stop's cache
+
+    @property
+    def pages(self) -> Optional[torch.Tensor]:
+        return self.kv_pages
 
 
 # ------------------------------------------------------------------ parts
 class Part:
     """Base of every part."""
 
+    # A part that launches only work a CUDA graph can record - no host reads of
+    # device data, and nothing that depends on the step's host-side lists
+    # (``ctx.segments``) other than through sizes that a graph key fixes - says
+    # so; decode steps of a model are replayed from a graph only if all its parts do.
+    graph_capturable = False
+
     def __init__(self, spec: PartSpec, prefix: str):
         self.spec = spec
         self.prefix = prefix
+
+    def children(self) -> List["Part"]:
+        return []
+
+    def step_plan_key(self) -> Optional[Hashable]:
+        """``None``: the part needs no step metadata of its own.  Parts that
+        return equal keys share one plan per step."""
+        return None
+
+    def plan_step(self, shape: StepShape) -> StepPlan:
+        raise NotImplementedError
 
     def name(self, local: str) -> str:
         return f"{self.prefix}.{local}" if self.prefix else local
@@ -172,7 +230,17 @@ class Norm(Part):
 
 
 class Position(Part):
-    pass
+    """What a mixer may ask of a position encoding: how many leading dims of a
+    head rotate (``rotary_dim``, 0: none), how they pair (``interleaved``:
+    ``(2i, 2i+1)``, else halves ``(i, i + rotary_dim/2)``), and the table
+    ``[>= positions, rotary_dim]`` of ``cos | sin`` per position in float32
+    (``None`` when nothing rotates)."""
+
+    rotary_dim: int = 0
+    interleaved: bool = False
+
+    def table(self, device, positions: int) -> Optional[torch.Tensor]:
+        return None
 
 
 class Mixer(Part):
@@ -189,16 +257,46 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    def __init__(self, spec: PartSpec, prefix: str, mixer: Mixer, feed_forward: FeedForward,
-                 mixer_norm: Norm, feed_forward_norm: Norm):
+    """A mixer, a feed-forward (or none) and norms by name.  A block kind states
+    the norms it arranges in ``NORM_NAMES`` and whether it has a feed-forward
+    in ``HAS_FEED_FORWARD``; the model builds exactly those from the layer's spec."""
+
+    NORM_NAMES: Tuple[str, ...] = ("mixer", "feed_forward")
+    HAS_FEED_FORWARD = True
+
+    def __init__(self, spec: PartSpec, prefix: str, mixer: Mixer, feed_forward: Optional[FeedForward],
+                 norms: Dict[str, Norm]):
         super().__init__(spec, prefix)
         self.mixer = mixer
         self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+        self.norms = dict(norms)
+
+    @classmethod
+    def check_parts(cls, prefix: str, norm_names: Sequence[str], has_feed_forward: bool) -> None:
+        if sorted(norm_names) != sorted(cls.NORM_NAMES):
+            raise ValueError(f"layer '{prefix}': a '{cls.__name__}' block arranges the norms "
+                             f"{sorted(cls.NORM_NAMES)}, the layer lists {sorted(norm_names)}")
+        if has_feed_forward != cls.HAS_FEED_FORWARD:
+            raise ValueError(f"layer '{prefix}': a '{cls.__name__}' block "
+                             f"{'needs' if cls.HAS_FEED_FORWARD else 'has no'} feed-forward")
+
+    @property
+    def mixer_norm(self) -> Norm:
+        return self.norms["mixer"]
+
+    @property
+    def feed_forward_norm(self) -> Norm:
+        return self.norms["feed_forward"]
+
+    @property
+    def graph_capturable(self) -> bool:       # a block records what its parts record
+        return True
 
     def children(self) -> List[Part]:
-        return [self.mixer, self.feed_forward, self.mixer_norm, self.feed_forward_norm]
+        out: List[Part] = [self.mixer]
+        if self.feed_forward is not None:
+            out.append(self.feed_forward)
+        return out + [self.norms[name] for name in sorted(self.norms)]
 
     def tensor_specs(self) -> List[TensorSpec]:
         out: List[TensorSpec] = []

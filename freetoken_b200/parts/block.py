@@ -18,6 +18,9 @@ from .base import Block, register_block
 
 @register_block("prenorm")
 class PreNormBlock(Block):
+    NORM_NAMES = ("mixer", "feed_forward")
+    HAS_FEED_FORWARD = True
+
     def forward(self, ctx, delta, residual, cache):
         h = self.mixer_norm.forward(ctx, delta, residual)
         a = self.mixer.forward(ctx, h, cache)

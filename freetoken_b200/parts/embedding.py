@@ -22,6 +22,8 @@ from .base import Embedding, Head, StepContext, register_embedding, register_hea
 class TokenEmbedding(Embedding):
     """params: ``vocab_size, hidden_size, scope``."""
 
+    graph_capturable = True
+
     def __init__(self, spec, prefix):
         super().__init__(spec, prefix)
         self.vocab = int(spec.params["vocab_size"])
@@ -46,6 +48,8 @@ class TokenEmbedding(Embedding):
 class LMHead(Head):
     """params: ``vocab_size, hidden_size, scope``, ``tied_to`` (full name of
     the embedding table, or None)."""
+
+    graph_capturable = True
 
     def __init__(self, spec, prefix):
         super().__init__(spec, prefix)

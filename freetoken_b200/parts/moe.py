@@ -64,6 +64,8 @@ class RoutedExperts(FeedForward):
     (router, bias, gate_up, down: model-side names below the scope; gate, up,
     down_each: per-expert checkpoint names with ``{e}``)."""
 
+    graph_capturable = True
+
     def __init__(self, spec, prefix):
         super().__init__(spec, prefix)
         p = spec.params

@@ -22,6 +22,8 @@ from .base import Norm, StepContext, register_norm
 class RMSNorm(Norm):
     """params: ``size``, ``eps``, ``plus_one``, ``scope`` (tensor name below the prefix)."""
 
+    graph_capturable = True
+
     def __init__(self, spec, prefix):
         super().__init__(spec, prefix)
         self.size = int(spec.params["size"])

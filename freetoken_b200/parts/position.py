@@ -39,6 +39,7 @@ def rotary_table(rotary_dim: int, theta: float, device, positions: int) -> torch
 
 
 class _Rotary(Position):
+    graph_capturable = True
     interleaved = False
 
     def __init__(self, spec, prefix):
@@ -70,6 +71,7 @@ class RotaryInterleaved(_Rotary):
 
 @register_position("none")
 class NoPosition(Position):
+    graph_capturable = True
     interleaved = False
     rotary_dim = 0
 

@@ -27,10 +27,6 @@ def make_ctx(dtype, segments, page, tokens=None):
     i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
     pos = [p for p0, n in segments for p in range(p0, p0 + n)]
     seg_of = [i for i, (_, n) in enumerate(segments) for _ in range(n)]
-    dec = [s.q_start for s in segs if s.n == 1]
-    pre = [r for s in segs if s.n > 1 for r in range(s.q_start, s.q_start + s.n)]
-    tiles = [(i, q0) for i, s in enumerate(segs) if s.n > 1 for q0 in range(0, s.n, 64)]
-    mixed = bool(dec) and bool(pre)
     ctx = StepContext(
         device=torch.device(DEV), dtype=DT[dtype], segments=segs, num_tokens=T,
         token_ids=i32(tokens if tokens is not None else [0] * T), token_pos=i32(pos), token_seg=i32(seg_of),
@@ -38,11 +34,7 @@ def make_ctx(dtype, segments, page, tokens=None):
         seg_q_start=i32([s.q_start for s in segs] + [T]), seg_kv_len=i32([s.pos0 + s.n for s in segs]),
         block_tables=[table.to(DEV)], workspace=Workspace(DEV), page_size=page,
         max_q_len=max(n for _, n in segments), max_kv_len=max(p0 + n for p0, n in segments),
-        max_positions=256, decode_rows=i32(dec) if mixed else None, prefill_rows=i32(pre) if mixed else None,
-        num_decode_rows=len(dec), num_prefill_rows=len(pre),
-        max_decode_kv_len=max([s.pos0 + 1 for s in segs if s.n == 1], default=0),
-        prefill_tile_seg=i32([t[0] for t in tiles]), prefill_tile_q0=i32([t[1] for t in tiles]),
-        num_prefill_tiles=len(tiles))
+        max_positions=256)          # a part that plans step metadata does so at its first use
     return ctx, pages
 
 
