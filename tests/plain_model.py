@@ -5,14 +5,16 @@ CPU.  It shares no code with ``freetoken_b200``: it reads ``config.json`` and
 ``model.safetensors`` itself and is written from the reference's formulas, each
 cited as ``file:line`` below (paths inside TaoLe-si/FreeToken).
 
-It rests on the formulas, not on a run of the reference: the reference's model
-code cannot run here.  ``import freetoken.models`` needs the absent ``flashlib``
-package, its norm / rotary / attention / expert ops call FlashInfer or Triton
-kernels that need a GPU, its rotary module refuses head sizes other than
-64/128/256/512 (python/freetoken/layers/rotary.py:60), and its ``minimax_m3``
-module hard-wires options this decoder reads from config.json.  The two pieces
-of the reference that do run on a CPU (the router's ``_route`` and the rotary
-table) are compared once in ``tests/golden/``.
+The reference's model code cannot run here as a whole: ``import
+freetoken.models`` needs the absent ``flashlib`` package, its rotary module
+refuses head sizes other than 64/128/256/512 (python/freetoken/layers/rotary.py:60),
+and its ``minimax_m3`` module hard-wires options this decoder reads from
+config.json.  Its pieces do run, and every part below is compared with them
+once (``tests/golden/``, ``tests/test_plain_model.py``): the router's ``_route``
+and the rotary table on the CPU, and - run once on a GPU - the reference's own
+Triton kernels for the rotation (both pairings), the add + RMSNorm (plain and
+1+w, per-head), the gated activations, paged causal attention and the whole
+``fused_experts_impl``.
 
 Precision: ``compute="float32"`` does everything in float32 on the stored
 values.  ``compute="bfloat16"`` rounds activations to bfloat16 wherever a
@@ -181,12 +183,15 @@ def glu(g: torch.Tensor, u: torch.Tensor, act: str, alpha: float, limit: float) 
 
 def experts(h: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, gate_up: List[torch.Tensor],
             down: List[torch.Tensor], act: str, alpha: float, limit: float,
-            round_to) -> torch.Tensor:
+            round_to, round_gate_up=None) -> torch.Tensor:
     """y_t = sum_j w_tj * Wdown_e ( act(Wgate_e h_t) * (Wup_e h_t) ), e = ids_tj.
     [gate; up] halves un-interleaved, python/freetoken/layers/activation.py:50-53;
     the route weight multiplies the float32 product before rounding,
     python/freetoken/kernel/triton/fused_moe.py:292-296; the k terms are summed in
-    float32, fused_moe.py:143-153."""
+    float32, fused_moe.py:143-153.  ``round_gate_up`` (when given) rounds the
+    [gate; up] product before the activation, as the reference does by storing it
+    in the activation dtype (python/freetoken/moe/fused.py:268-300); the engine's
+    kernels feed the activation from the float32 accumulator instead."""
     T, H = h.shape
     out = torch.zeros(T, H, dtype=torch.float32)
     for t in range(T):
@@ -194,6 +199,8 @@ def experts(h: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, gate_up: List[t
         for j in range(ids.shape[1]):
             e = int(ids[t, j])
             gu = gate_up[e].float() @ h[t].float()
+            if round_gate_up is not None:
+                gu = round_gate_up(gu)
             inter = gu.shape[0] // 2
             m = round_to(glu(gu[:inter], gu[inter:], act, alpha, limit))
             y = round_to((down[e].float() @ m.float()) * w[t, j])
