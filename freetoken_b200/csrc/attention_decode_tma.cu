@@ -11,6 +11,13 @@
 //              mma.sync, and arrive on the stage's "empty" mbarrier - no block-wide
 //              barrier inside the loop, no per-thread address arithmetic or cp.async
 //
+// With up to 8 splits the CTAs of a (row, KV head) form a thread-block CLUSTER along
+// the split axis and merge among themselves: each leaves its partial result in its own
+// shared memory, and after a cluster barrier every CTA reads its share of (head, dim)
+// pairs from all of them through distributed shared memory, in split order - no partials
+// in global memory and no merge kernel.  More splits than a cluster holds (long contexts)
+// write partials for attn_merge as before.
+//
 // Needs head size 64 or 128 and a page size that is a multiple of 64 (a tile then
 // lies inside one page); other shapes use attention_decode.cu.  Every mbarrier wait
 // is bounded (about two seconds): on expiry the CTA writes a code into `status`
@@ -18,6 +25,7 @@
 //
 // Reference: split-KV grouped decode in two stages,
 // python/freetoken/kernel/triton/attention.py:147-349; scale and mask :74,118-139.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include <cstring>
@@ -48,7 +56,7 @@ constexpr int DT_STAGES = 3;
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int D>
+template <int D, bool CLUSTER>
 __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_kv,
                                                               DecodeTmaArgs a) {
   constexpr int TILE = DT_TILE, STAGES = DT_STAGES;
@@ -126,6 +134,11 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
                  global_ns() - t0 < 100000000ull) {}
         }
       }
+    }
+    if (CLUSTER) {
+      // stay for the cluster's two barriers: the others read this CTA's shared memory
+      cooperative_groups::this_cluster().sync();
+      cooperative_groups::this_cluster().sync();
     }
     return;
   }
@@ -271,6 +284,9 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
     red_ml[(warp * 16 + g + 8) * 2 + 1] = l1;
   }
   consumer_sync();
+  // this CTA's result per (head row, dim): unnormalised sum, max (log2 domain) and weight sum
+  float* xo = red_ml + 4 * 16 * 2;                      // [16][D]   (cluster exchange)
+  float* xml = xo + 16 * D;                             // [16][2]
   for (int idx = tid; idx < heads * D; idx += 128) {
     const int r = idx / D, c = idx % D;
     float m = -INFINITY;
@@ -285,7 +301,13 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
       acc += red_o[(w * 16 + r) * D + c] * f;
     }
     const int head = head0 + r;
-    if (a.splits == 1) {
+    if (CLUSTER) {
+      xo[r * D + c] = acc;
+      if (c == 0) {
+        xml[r * 2] = m;
+        xml[r * 2 + 1] = l;
+      }
+    } else if (a.splits == 1) {
       a.out[((size_t)tok * a.nq + head) * D + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     } else {
       const size_t pi = ((size_t)row * a.nq + head) * a.splits + split;
@@ -296,8 +318,37 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
       }
     }
   }
+  if (CLUSTER) {
+    // out[head, c] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m), splits ascending; the
+    // (head, dim) pairs are dealt out over the cluster's CTAs, each reads every CTA's share
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int nsplit = a.splits, me = split;            // cluster = the splits of this (row, head tile)
+    const int total = heads * D;
+    const int share = (total + nsplit - 1) / nsplit;
+    for (int idx = me * share + tid; idx < min(total, (me + 1) * share); idx += 128) {
+      const int r = idx / D, c = idx % D;
+      float m = -INFINITY;
+      for (int s2 = 0; s2 < nsplit; ++s2) m = fmaxf(m, cluster.map_shared_rank(xml, s2)[r * 2]);
+      float l = 0.f, acc = 0.f;
+      for (int s2 = 0; s2 < nsplit; ++s2) {
+        const float* rml = cluster.map_shared_rank(xml, s2);
+        const float ms = rml[r * 2];
+        if (ms != -INFINITY) {
+          const float f = fast_exp2(ms - m);
+          l += rml[r * 2 + 1] * f;
+          acc += cluster.map_shared_rank(xo, s2)[r * D + c] * f;
+        }
+      }
+      a.out[((size_t)tok * a.nq + head0 + r) * D + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+    cluster.sync();        // nobody leaves while its shared memory may still be read
+  }
 }
 
+
+constexpr int DT_MAX_CLUSTER = 8;      // portable cluster size
 
 template <int D>
 int launch_decode_tma(const CUtensorMap& mkv, const DecodeTmaArgs& a, cudaStream_t stream) {
@@ -305,13 +356,34 @@ int launch_decode_tma(const CUtensorMap& mkv, const DecodeTmaArgs& a, cudaStream
   const size_t smem = (size_t)DT_STAGES * 2 * (D / 64) * DT_TILE * 128 + 16 * (D + 8) * sizeof(__nv_bfloat16) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   dim3 grid(a.n_rows, a.nkv * ((G + 15) / 16), a.splits);
-  launch_pdl(attn_decode_tma_kernel<D>, grid, dim3(160), smem, stream, mkv, a);
+  if (a.splits > 1 && a.splits <= DT_MAX_CLUSTER && !a.part_o) {
+    // the splits of a (row, head tile) as one cluster along z
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(160);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = (unsigned)a.splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_tma_kernel<D, true>, mkv, a);
+    return e == cudaSuccess ? FT_OK : (int)e;
+  }
+  launch_pdl(attn_decode_tma_kernel<D, false>, grid, dim3(160), smem, stream, mkv, a);
   return FT_OK;
 }
 
@@ -320,8 +392,9 @@ int launch_decode_tma(const CUtensorMap& mkv, const DecodeTmaArgs& a, cudaStream
 using namespace ft;
 
 // bfloat16; head_dim 64 or 128; page size a multiple of 64.  `map_kv`: the 5-D map
-// over the layer's pages (ft_attn_tc_kv_map of the prefill library).  part_o /
-// part_ml are needed when splits > 1; the caller merges them with ft_attn_merge.
+// over the layer's pages (ft_attn_tc_kv_map of the prefill library).  Up to 8 splits
+// are merged inside the kernel by a cluster when part_o is null; otherwise part_o /
+// part_ml receive the partials and the caller merges them with ft_attn_merge.
 extern "C" int ft_attn_decode_tma(const void* map_kv, const void* q, void* out, float* part_o,
                                   float* part_ml, const int* rows, const int* token_pos,
                                   const int* token_seg, const int* block_table, int* status, int nq,
@@ -330,7 +403,7 @@ extern "C" int ft_attn_decode_tma(const void* map_kv, const void* q, void* out, 
   if (n_rows <= 0) return FT_OK;
   if (nkv <= 0 || nq % nkv || splits < 1 || split_keys < DT_TILE || split_keys % DT_TILE || P % DT_TILE)
     return FT_ERR_SHAPE;
-  if (splits > 1 && (!part_o || !part_ml)) return FT_ERR_SHAPE;
+  if (splits > DT_MAX_CLUSTER && (!part_o || !part_ml)) return FT_ERR_SHAPE;
   CUtensorMap mkv;
   memcpy(&mkv, map_kv, sizeof(mkv));
   DecodeTmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, part_o, part_ml, rows, token_pos,

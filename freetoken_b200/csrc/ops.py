@@ -498,17 +498,26 @@ def attn_decode_takes(q: torch.Tensor, head_dim: int) -> bool:
 # Decode attention with K/V tiles fetched by TMA where the shapes allow it
 # (FREETOKEN_DECODE_TMA=0: always the cp.async kernel).
 DECODE_TMA = os.environ.get("FREETOKEN_DECODE_TMA", "1") not in ("", "0")
+# ... and up to eight splits merged inside that kernel by a thread-block cluster
+# (FREETOKEN_DECODE_CLUSTER=0: partials in global memory and the merge kernel).
+DECODE_CLUSTER = os.environ.get("FREETOKEN_DECODE_CLUSTER", "1") not in ("", "0")
 
 
-def decode_splits(n_rows: int, num_kv_heads: int, group: int, max_kv_len: int, sms: int):
+CLUSTER_SPLITS = 8     # splits the TMA-fed decode kernel merges by itself (a thread-block cluster)
+MERGE_COST = 24        # what the separate merge kernel costs, in 64-key tiles of a CTA's work
+
+
+def decode_splits(n_rows: int, num_kv_heads: int, group: int, max_kv_len: int, sms: int,
+                  cluster_merge: bool = False):
     """``(splits, keys per split)``, whole 64-key tiles per split.
 
     Two CTAs of the decode kernel fit an SM and a launch takes as long as its
     rounds of CTAs: rounds x (tiles per split + a CTA's fixed cost, about three
-    tiles' worth: query load, pipeline fill, partial write and its merge).  The
-    split count with the least such time is taken, the smaller one on a tie -
-    not just "enough CTAs to fill the SMs", which leaves a second round nearly
-    empty at some sizes."""
+    tiles' worth: query load, pipeline fill, partial write).  The split count with
+    the least such time is taken, the smaller one on a tie - not just "enough
+    CTAs to fill the SMs", which leaves a second round nearly empty at some
+    sizes.  With ``cluster_merge`` up to :data:`CLUSTER_SPLITS` splits are merged
+    inside the kernel; more need the merge kernel, whose launch is counted."""
     base = max(1, n_rows * num_kv_heads * (-(-group // 16)))
     tiles = max(1, -(-max_kv_len // 64))
     slots = 2 * sms
@@ -520,6 +529,8 @@ def decode_splits(n_rows: int, num_kv_heads: int, group: int, max_kv_len: int, s
             continue                      # the same split as a smaller request
         rounds = -(-base * splits // slots)
         cost = rounds * (per + 3)
+        if cluster_merge and splits > CLUSTER_SPLITS:
+            cost += MERGE_COST
         if best_cost is None or cost < best_cost:
             best, best_cost = splits, cost
     per = -(-tiles // best)
@@ -541,14 +552,15 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
         _need(t, name, torch.int32)
     if rows is not None:
         _need(rows, "rows", torch.int32)
+    tma = DECODE_TMA and head_dim in (64, 128) and kv_pages.shape[3] % 64 == 0 \
+        and kv_pages.stride(4) == 1 and kv_pages.stride(3) == head_dim
     splits, split_keys = decode_splits(n_rows, num_kv_heads, num_heads // num_kv_heads, max_kv_len,
-                                       sm_count(q.device))
+                                       sm_count(q.device), cluster_merge=tma and DECODE_CLUSTER)
     part_o = part_ml = None
-    if splits > 1:
+    if splits > 1 and not (tma and DECODE_CLUSTER and splits <= CLUSTER_SPLITS):
         part_o = workspace.get("attn.part_o", (n_rows, num_heads, splits, head_dim), torch.float32)
         part_ml = workspace.get("attn.part_ml", (n_rows, num_heads, splits, 2), torch.float32)
-    if DECODE_TMA and head_dim in (64, 128) and kv_pages.shape[3] % 64 == 0 \
-            and kv_pages.stride(4) == 1 and kv_pages.stride(3) == head_dim:
+    if tma:
         # K and V tiles by TMA: a tile lies inside one page
         lib = build.load("attention_prefill_tc")
 
@@ -565,7 +577,7 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
                  _ptr(rows), _ptr(token_pos), _ptr(token_seg), _ptr(block_table), _ptr(tc_status(q.device)),
                  num_heads, num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1],
                  int(window or 0), n_rows, splits, split_keys, float(scale), _stream()), "attn_decode_tma")
-        if splits > 1:
+        if part_o is not None:
             fm = _fn("attention_decode", "ft_attn_merge", "p p p p i i i i")
             _check(fm(_ptr(part_o), _ptr(part_ml), _ptr(out), _ptr(rows), n_rows, num_heads, head_dim,
                       splits, _stream()), "attn_merge")

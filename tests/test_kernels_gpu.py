@@ -518,15 +518,17 @@ def test_attn_decode(nq, nkv, d, P, positions, window, standout):
     assert torch.allclose(out.float().cpu(), want, **TOL["bfloat16"])
     o.check_tc_status(DEV)
     if d in (64, 128) and P % 64 == 0:
-        # the same through the cp.async kernel
-        out3 = torch.zeros_like(q)
-        o.DECODE_TMA = False
-        try:
-            o.attn_decode(q, out3, kv, None, len(positions), pos, seg, table, nq, nkv, d, scale, window,
-                          max(positions) + 1, Workspace(DEV))
-        finally:
-            o.DECODE_TMA = True
-        assert torch.allclose(out3.float().cpu(), want, **TOL["bfloat16"])
+        # the same through the cp.async kernel, and through the TMA-fed kernel with the
+        # splits merged by the separate kernel instead of by a cluster
+        for name in ("DECODE_TMA", "DECODE_CLUSTER"):
+            out3 = torch.zeros_like(q)
+            setattr(o, name, False)
+            try:
+                o.attn_decode(q, out3, kv, None, len(positions), pos, seg, table, nq, nkv, d, scale, window,
+                              max(positions) + 1, Workspace(DEV))
+            finally:
+                setattr(o, name, True)
+            assert torch.allclose(out3.float().cpu(), want, **TOL["bfloat16"]), name
     # a subset of rows through the row list leaves the other rows alone
     if len(positions) > 1:
         rows = torch.tensor([len(positions) - 1], dtype=torch.int32, device=DEV)
