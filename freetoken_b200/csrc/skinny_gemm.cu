@@ -64,9 +64,10 @@ __device__ __forceinline__ float glu_act_s(float g, float u, int act, float alph
   return (g / (1.f + __expf(-alpha * g))) * (u + 1.f);
 }
 
-// KS: warps per block, splitting K.  4 for the experts' gate_up bank and the head
-// (many blocks), 2 for the experts' down projection (short rows: 1,536 values; two
-// warps keep a warp's stream of a row twice as long and measured 3-5 % faster);
+// KS: warps per block, splitting K.  2 for the experts (gate_up bank: measured against 4
+// warps, 26.3 instead of 29.8 us for the eight experts of a single token and level from
+// batch 8 on; 1 and 8 are slower; down projection, rows of 1,536 values: two warps keep
+// a warp's stream of a row twice as long and measured 3-5 % faster than four);
 // 8 or 16 for dense matrices with few rows (QKV, O), where 4 warps per
 // 16 weight rows would leave an SM with a handful of warps and too few loads in
 // flight to fill the memory pipe.  KS is chosen from the weight's shape alone.
@@ -201,15 +202,17 @@ int launch_nt(const SkinnyArgs& a, int nt, dim3 grid, cudaStream_t stream) {
 
 // Warps per block for a dense [N, K] weight: 2 when there are blocks in plenty
 // anyway (measured 4 % faster on the head), else doubled from 4 while the launch
-// would hold fewer than about 20 warps per SM and a warp keeps at least 8
-// chunks of 32 k.  A function of the weight's shape only, so a token's result
-// does not depend on what else is in the batch.
+// would hold fewer than about 1,500 warps and a warp keeps at least 8 chunks of
+// 32 k.  Measured on a B200 at batch 1 / 8 (weights cold): QKV [8192 x 3072] 11.1 /
+// 12.1 us with 4 warps (8: 12.5 / 13.9, 2: 14.4, 16: 15.5); O [3072 x 6144] 9.8 /
+// 10.9 us with 8 warps (16: 11.6 / 12.1, 4: 14.7).  A function of the weight's shape
+// only, so a token's result does not depend on what else is in the batch.
 static int dense_k_split(int N, int K) {
   const long long tiles = (N + 15) / 16;
   const int chunks = (K + 31) / 32;
   int ks = 4;
   if (tiles * 2 >= 6000) return 2;      // blocks in plenty (the head): long streams per warp
-  while (ks < 16 && tiles * ks < 3000 && chunks / (2 * ks) >= 8) ks *= 2;
+  while (ks < 16 && tiles * ks < 1500 && chunks / (2 * ks) >= 8) ks *= 2;
   return ks;
 }
 
@@ -241,13 +244,13 @@ extern "C" int ft_skinny_gemm(const void* A, long long lda, const void* W,
   // of a row long enough (a function of the weight's shape, like the dense choice)
   if (!glu && group_offsets && K <= 2048) ks = 2;
   if (c_dtype == FT_DTYPE_BF16) {
-    if (glu) rc = launch_nt<true, __nv_bfloat16, 4>(a, nt, grid, stream);
+    if (glu) rc = launch_nt<true, __nv_bfloat16, 2>(a, nt, grid, stream);
     else if (ks == 2) rc = launch_nt<false, __nv_bfloat16, 2>(a, nt, grid, stream);
     else if (ks == 16) rc = launch_nt<false, __nv_bfloat16, 16>(a, nt, grid, stream);
     else if (ks == 8) rc = launch_nt<false, __nv_bfloat16, 8>(a, nt, grid, stream);
     else rc = launch_nt<false, __nv_bfloat16, 4>(a, nt, grid, stream);
   } else if (c_dtype == FT_DTYPE_F32) {
-    if (glu) rc = launch_nt<true, float, 4>(a, nt, grid, stream);
+    if (glu) rc = launch_nt<true, float, 2>(a, nt, grid, stream);
     else if (ks == 2) rc = launch_nt<false, float, 2>(a, nt, grid, stream);
     else if (ks == 16) rc = launch_nt<false, float, 16>(a, nt, grid, stream);
     else if (ks == 8) rc = launch_nt<false, float, 8>(a, nt, grid, stream);
