@@ -153,6 +153,22 @@ def prefill_flops(cfg: Dict[str, Any], layers: int, tokens: int) -> float:
     return layers * (per_token * tokens + attn) + 2 * V * H
 
 
+def measure_read_peak(timed, gib: int = 2) -> float:
+    """GB/s of a load-only kernel over ``gib`` GiB (larger than L2), best of 3 runs of 5."""
+    import torch
+
+    from .csrc import ops
+    buf = torch.empty(gib << 30, dtype=torch.uint8, device="cuda")
+    buf.view(torch.int32).random_(0, 1 << 20)
+    partial = torch.empty(8 * ops.sm_count(buf.device), dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        ops.read_sum(buf, partial)
+    best = min(timed(lambda: ops.read_sum(buf, partial), 5) for _ in range(3))
+    del buf
+    torch.cuda.empty_cache()
+    return (gib << 30) / (best / 1e3) / 1e9
+
+
 def equivalence(a) -> int:
     """The float32 path against the bfloat16 path at real width: same seed, same
     token ids, logits at 15 prompt positions and at 8 decoded tokens."""
@@ -211,6 +227,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
     p.add_argument("--prefill-tokens", type=int, default=2048)
+    p.add_argument("--prefill-requests", type=int, default=1,
+                   help="prompts of --prefill-tokens tokens in the timed prefill step")
     p.add_argument("--points", default="1,64", help="further decode batch sizes")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--seed", type=int, default=0)
@@ -250,13 +268,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     max_batch = max(batches)
     page = 64
     room = a.context + a.steps + a.warmup + 2 * page
-    pool_tokens = max_batch * (-(-room // page) * page) + (-(-a.prefill_tokens // page) * page)
+    pool_tokens = max_batch * (-(-room // page) * page) + a.prefill_requests * (-(-a.prefill_tokens // page) * page)
     cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], room + page)
     peaks = load_peaks()
     t0 = time.time()
     llm = LLM("", a.dtype, config=cfg, use_dummy_weight=True, seed=a.seed,
               dummy_weight_options=bench_random_options(a.router_bias_std),
-              max_running_req=max_batch + 1, page_size=page, num_token_override=pool_tokens,
+              max_running_req=max_batch + a.prefill_requests, page_size=page, num_token_override=pool_tokens,
               max_extend_tokens=8192, max_seq_len_override=room + page)
     engine = llm.engine
     torch.cuda.synchronize()
@@ -276,30 +294,43 @@ def main(argv: Optional[List[str]] = None) -> int:
         torch.cuda.synchronize()
         return start.elapsed_time(end) / reps
 
+    # ---- the read-only stream this GPU reaches, measured in place -----------
+    # The driver's HBM peak is a copy (half reads, half writes); a decode step only reads.
+    # Every HBM fraction below is given against both.
+    read_gbs = measure_read_peak(timed)
+
     # ---- prefill: one prompt of --prefill-tokens tokens in one step -------
     def prefill_once():
-        toks = rng.integers(0, V, a.prefill_tokens).tolist()
-        logits = engine.step([StepEntry("prefill", toks, [len(toks) - 1])])
-        llm.sampler.sample(logits, [greedy], [0.0])
-        engine.end_request("prefill")
+        entries = []
+        for i in range(a.prefill_requests):
+            toks = rng.integers(0, V, a.prefill_tokens).tolist()
+            entries.append(StepEntry(("prefill", i), toks, [len(toks) - 1]))
+        logits = engine.step(entries)
+        llm.sampler.sample(logits, [greedy] * a.prefill_requests, [0.0] * a.prefill_requests)
+        for i in range(a.prefill_requests):
+            engine.end_request(("prefill", i))
 
     for _ in range(3):
         prefill_once()
     with ClockSampler() as prefill_clocks:
         prefill_ms = timed(prefill_once, 5)
-    pf = prefill_flops(cfg, layers, a.prefill_tokens)
+    pf = a.prefill_requests * prefill_flops(cfg, layers, a.prefill_tokens)
     # what bounds this step: a 2,048-token portion sends a few dozen rows to each of
     # the experts it touches, so their weights are read for a few rows each; hbm_frac is
     # the weight bytes of the step (experts counted from the router in an untimed probe
     # step, as for decode) over its time
     pf_probe: Dict[str, Any] = {}
-    engine.step([StepEntry("prefill", rng.integers(0, V, a.prefill_tokens).tolist(), [])], probe=pf_probe)
-    engine.end_request("prefill")
+    engine.step([StepEntry(("prefill", i), rng.integers(0, V, a.prefill_tokens).tolist(), [])
+                 for i in range(a.prefill_requests)], probe=pf_probe)
+    for i in range(a.prefill_requests):
+        engine.end_request(("prefill", i))
     pf_touched = pf_probe.get("experts_touched", [cfg["num_local_experts"]] * layers)
     pf_bytes = step_bytes(cfg, layers, 1, a.prefill_tokens, pf_touched)
-    prefill = {"value": a.prefill_tokens / (prefill_ms / 1e3), "tokens": a.prefill_tokens,
+    prefill = {"value": a.prefill_requests * a.prefill_tokens / (prefill_ms / 1e3),
+               "tokens": a.prefill_requests * a.prefill_tokens, "requests": a.prefill_requests,
                "ms": prefill_ms, "frac": pf / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12),
                "hbm_frac": pf_bytes / (prefill_ms / 1e3) / (peaks["hbm_gbs"] * 1e9),
+               "hbm_frac_of_read_peak": pf_bytes / (prefill_ms / 1e3) / (read_gbs * 1e9),
                "experts_touched_per_layer": sum(pf_touched) / max(1, len(pf_touched))}
 
     # ---- decode at each batch size -----------------------------------------
@@ -411,10 +442,12 @@ def main(argv: Optional[List[str]] = None) -> int:
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": main_r["gbs"], "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": main_r["gbs"] / peaks["hbm_gbs"],
-                     "peaks": peaks["source"], "bytes_per_step": main_r["bytes"],
+                     "peaks": peaks["source"], "read_peak": read_gbs,
+                     "frac_of_read_peak": main_r["gbs"] / read_gbs, "bytes_per_step": main_r["bytes"],
                      "experts_touched_per_layer": (sum(touched_main) / max(1, len(touched_main)))},
         "points": {f"decode_b{b}": results[b]["tok_s"] for b in batches if b != a.batch},
         "points_roofline_frac": {f"decode_b{b}": results[b]["gbs"] / peaks["hbm_gbs"] for b in batches},
+        "points_frac_of_read_peak": {f"decode_b{b}": results[b]["gbs"] / read_gbs for b in batches},
         "clocks": clocks_main,
         "prefill_clocks": prefill_clocks.summary(),
         "context_build": context_build,

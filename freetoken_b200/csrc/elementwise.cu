@@ -444,6 +444,39 @@ __global__ void gather_rows_kernel(const AT* __restrict__ src, const int* __rest
   for (int i = threadIdx.x; i < H; i += blockDim.x) d[i] = s[i];
 }
 
+// ------------------------------------------------------------ read stream
+// Sums a buffer of 16-byte words: nothing but loads, eight in flight per thread.
+// What a read-only stream reaches on this GPU - the ceiling of a decode step, which
+// reads weights and cache and writes next to nothing (a copy, the usual yardstick,
+// spends half of its traffic on writes).  partial[block] receives the block's sum.
+__global__ void __launch_bounds__(256) read_sum_kernel(const uint4* __restrict__ src, long long n16,
+                                                       unsigned* __restrict__ partial) {
+  __shared__ unsigned red[256];
+  unsigned acc = 0;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 7 * stride < n16; i += 8 * stride) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w) : "l"(src + i + u * stride));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc += v[u].x ^ v[u].y ^ v[u].z ^ v[u].w;
+  }
+  for (; i < n16; i += stride) {
+    const uint4 v = src[i];
+    acc += v.x ^ v.y ^ v.z ^ v.w;
+  }
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) partial[blockIdx.x] = red[0];
+}
+
 // ids[rows[i]] = src[src_index[i]]: the tokens a step sampled become the next
 // step's inputs without a round trip through the host.  An id outside the
 // vocabulary (which the sampler never writes) becomes 0.
@@ -532,6 +565,15 @@ int ft_qk_rope_store(const void* qkv, void* q_out, void* kv_pages, const float* 
 int ft_combine(const void* parts, void* out, int dtype, int T, int k, int H, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   FT_DISPATCH(dtype, AT, launch_pdl(combine_kernel<AT>, dim3(T), dim3(256), 0, stream, (const AT*)parts, (AT*)out, k, H));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+// Reads `bytes` (a multiple of 16, 16-byte aligned) once; `partial` holds `blocks` words.
+int ft_read_sum(const void* src, long long bytes, unsigned* partial, int blocks, cudaStream_t stream) {
+  if (bytes <= 0 || blocks <= 0) return FT_OK;
+  if ((bytes & 15) || ((uintptr_t)src & 15)) return FT_ERR_SHAPE;
+  read_sum_kernel<<<blocks, 256, 0, stream>>>((const uint4*)src, bytes >> 4, partial);
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

@@ -196,6 +196,16 @@ def combine(parts: torch.Tensor, out: torch.Tensor, k: int) -> None:
     _check(f(_ptr(parts), _ptr(out), code(out.dtype), T, k, H, _stream()), "combine")
 
 
+def read_sum(src: torch.Tensor, partial: torch.Tensor) -> None:
+    """Stream ``src`` once (loads only) and leave a checksum per block in ``partial``
+    (int32, one word per block: the grid): the measure of the GPU's read bandwidth."""
+    _need(src, "src")
+    _need(partial, "partial", torch.int32)
+    nbytes = src.numel() * src.element_size()
+    f = _fn("elementwise", "ft_read_sum", "p q p i")
+    _check(f(_ptr(src), nbytes, _ptr(partial), partial.numel(), _stream()), "read_sum")
+
+
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, dst: torch.Tensor) -> None:
     _need(src, "src")
     _need(rows, "rows", torch.int32)

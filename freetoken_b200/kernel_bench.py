@@ -14,7 +14,8 @@ experts on tcgen05/TMEM with TMA), ``attn_decode`` (64 rows x 2,048 keys; ``_32k
 ``router`` (float32 router logits + top-k for a decode batch); ``*_flashinfer``: the same
 attention shapes through FlashInfer's trtllm-gen kernels (the reference's backend on
 this GPU), as a comparison point; ``peak_copy`` / ``peak_gemm``: a 1 GiB device copy and an
-8192^3 library bf16 product, the two roofline denominators measured in place.
+8192^3 library bf16 product, the two roofline denominators measured in place; ``peak_read``:
+a 4 GiB read-only stream, the tighter ceiling of a decode step.
 """
 
 from __future__ import annotations
@@ -218,6 +219,15 @@ def peak_copy():
     return (lambda i: b.copy_(a)), 2 * n, 0.0, "hbm"
 
 
+def peak_read(gib: int = 4):
+    """A read-only stream over 4 GiB (our own load-only kernel): the ceiling of a step that
+    reads weights and cache and writes almost nothing."""
+    a = torch.empty(gib << 30, dtype=torch.uint8, device=DEV)
+    a.view(torch.int32).random_(0, 1 << 20)
+    partial = torch.empty(8 * ops.sm_count(DEV), dtype=torch.int32, device=DEV)
+    return (lambda i: ops.read_sum(a, partial)), gib << 30, 0.0, "hbm"
+
+
 def peak_gemm():
     n = 8192
     a = torch.randn(n, n, device=DEV, dtype=torch.bfloat16)
@@ -244,7 +254,7 @@ KERNELS: Dict[str, Callable[[], Tuple[Callable[[int], None], int, float, str]]] 
     "expert_gemv": expert_gemv, "lm_head": lm_head, "moe_gemm_tc": moe_gemm_tc,
     "attn_decode": attn_decode, "attn_decode_32k": attn_decode_32k, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
     "attn_prefill_8k": attn_prefill_8k, "attn_prefill_tc_8k": attn_prefill_tc_8k, "router": router,
-    "peak_copy": peak_copy, "peak_gemm": peak_gemm,
+    "peak_copy": peak_copy, "peak_read": peak_read, "peak_gemm": peak_gemm,
     "attn_decode_flashinfer": attn_decode_flashinfer, "attn_decode_32k_flashinfer": attn_decode_32k_flashinfer,
     "attn_prefill_flashinfer": attn_prefill_flashinfer, "attn_prefill_8k_flashinfer": attn_prefill_8k_flashinfer,
 }
