@@ -380,8 +380,11 @@ using namespace ft;
 
 extern "C" {
 
-// Tensor map over bfloat16 [groups, rows, K] (groups = 1 for a plain matrix)
-// with boxes of [box_rows, 64] in the 128-byte swizzle.  `out` receives 128 bytes.
+// Tensor map over bfloat16 rows with boxes of [box_rows, 64] in the 128-byte swizzle:
+// 3-D [groups, rows, K] for the expert weights (`groups` >= 1: the kernel addresses them
+// with three coordinates, one expert or many), 2-D [rows, K] for the token rows
+// (`groups` = 0).  The rank must be the rank of the load that uses the map: a 3-D load
+// through a 2-D map is an illegal instruction.  `out` receives 128 bytes.
 int ft_tc_make_map(void* out, const void* base, long long groups, long long rows, long long K,
                    long long row_stride, int box_rows) {
   EncodeTiledFn fn = encode_fn();
@@ -389,7 +392,7 @@ int ft_tc_make_map(void* out, const void* base, long long groups, long long rows
   if ((K & 7) || (row_stride & 7) || ((uintptr_t)base & 15) || box_rows < 1 || box_rows > 256) return FT_ERR_SHAPE;
   CUtensorMap map;
   CUresult rc;
-  if (groups > 1) {
+  if (groups >= 1) {
     cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)groups};
     cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)rows * (cuuint64_t)row_stride * 2};
     cuuint32_t box[3] = {TC_BK, (cuuint32_t)box_rows, 1};

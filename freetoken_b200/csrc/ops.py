@@ -239,8 +239,8 @@ def gemm_rows(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
     M = rows if rows is not None else a.shape[0]
     if a.shape[1] != K or c.shape[1] != N or a.stride(1) != 1 or c.stride(1) != 1:
         raise KernelError("gemm_rows: shapes do not match")
-    if (G > 1) != (group_offsets is not None):
-        raise KernelError("gemm_rows: group_offsets must be given exactly for grouped weights")
+    if (w.dim() == 3) != (group_offsets is not None):
+        raise KernelError("gemm_rows: group_offsets must be given exactly for grouped ([G, N, K]) weights")
     for name, t in (("group_offsets", group_offsets), ("a_rows", a_rows), ("c_rows", c_rows)):
         if t is not None:
             _need(t, name, torch.int32)
@@ -283,8 +283,8 @@ def skinny_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *,
         raise KernelError("skinny_gemm: shapes do not match")
     if not skinny_gemm_takes(a, w, c):
         raise KernelError("skinny_gemm: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
-    if (G > 1) != (group_offsets is not None):
-        raise KernelError("skinny_gemm: group_offsets must be given exactly for grouped weights")
+    if (w.dim() == 3) != (group_offsets is not None):
+        raise KernelError("skinny_gemm: group_offsets must be given exactly for grouped ([G, N, K]) weights")
     if rows_per_pass not in (8, 16, 32):
         raise KernelError("skinny_gemm: rows_per_pass must be 8, 16 or 32")
     if active is not None:
@@ -427,7 +427,7 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
         _need(t, name, torch.int32)
     ntok = tokens_per_tile or tc_tokens_per_tile(rows, G)
     map_w = _tc_map(w, NW, K, K, G, 128)
-    map_x = _tc_map(x, x.shape[0], K, x.stride(0), 1, ntok)
+    map_x = _tc_map(x, x.shape[0], K, x.stride(0), 0, ntok)      # 0: a 2-D map (token rows)
     status = tc_status(x.device)
     f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p p p i i i i i i i f f")
     _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(map_x, ctypes.c_void_p), _ptr(c),

@@ -189,7 +189,8 @@ def _grouped_case(E, k, T, seed=0):
 @pytest.mark.parametrize("E,k,T,H,I,act", [(4, 2, 5, 64, 32, "silu"), (8, 3, 19, 96, 48, "swigluoai"),
                                            (16, 4, 150, 128, 80, "silu"), (3, 1, 40, 40, 24, "silu"),
                                            (8, 2, 700, 264, 200, "silu"),
-                                           (4, 2, 650, 136, 72, "silu")])     # 325 rows per expert: wide tiles
+                                           (4, 2, 650, 136, 72, "silu"),      # 325 rows per expert: wide tiles
+                                           (1, 1, 300, 128, 80, "silu")])     # a single expert: still a 3-D weight map
 def test_expert_gemms(kernel, E, k, T, H, I, act):
     """gate_up + GLU, then down with the route weight, against a per-route loop."""
     o = ops()
