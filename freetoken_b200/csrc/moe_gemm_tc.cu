@@ -64,28 +64,55 @@ __device__ __forceinline__ float tc_glu(float g, float u, int act, float alpha, 
   return (g / (1.f + __expf(-alpha * g))) * (u + 1.f);
 }
 
+// Rows of one token tile of a group with `r` rows when tiles hold at most `ntok`: the
+// group's rows are dealt out evenly over the fewest tiles that hold them (in steps of
+// 16, the MMA's N granularity).  An expert with 280 rows and 256-row tiles gets two
+// tiles of 144 rather than one of 256 and one of 24 - the short tile would stream the
+// whole weight tile for a sliver of work.
+__host__ __device__ __forceinline__ int tc_tile_rows(int r, int ntok) {
+  const int nt = (r + ntok - 1) / ntok;
+  if (nt <= 1) return ntok;
+  const int sz = (((r + nt - 1) / nt) + 15) & ~15;
+  return sz < ntok ? sz : ntok;
+}
+
+// Kernel variants.
+//   TC_GLU2   gate_up + GLU, 128 output features per tile as TWO accumulators (128 gate
+//             rows, 128 up rows), up to 128 tokens: few rows per expert, where the step
+//             is bound by streaming each expert's weights once
+//   TC_PLAIN  no GLU, 128 weight rows x up to 128 tokens, two k-blocks per stage
+//   TC_WIDE   no GLU, 128 weight rows x up to 256 tokens
+// (A variant with gate and up rows side by side in ONE accumulator of up to 256 tokens -
+// an MMA of N = 256 reads less of A per flop from shared memory than two of N = 128 -
+// was built and measured: 642 instead of 392 us at 256 rows per expert; its epilogue,
+// which pairs TMEM lane f with lane f + 64 through shared memory, does not hide under
+// the main loop.)
+enum { TC_GLU2 = 0, TC_PLAIN = 1, TC_WIDE = 2 };
+
 // Persistent: one CTA per SM walks the tiles t = blockIdx.x, + gridDim.x, ...
 // of the (token tile, weight tile) space, weight tile fastest, so CTAs that run
 // side by side share an expert.  The TMA ring never drains between tiles and the
 // accumulator is double-buffered in TMEM, so the epilogue of one tile runs under
-// the main loop of the next.
-// WIDE (down projection with many rows per expert): token tiles of up to 256,
-// so a weight tile is fetched half as often per product: at 128 x 128 both
-// operands are re-read for every tile and the shared-memory fill, not the
-// tensor core, sets the pace.
-template <bool GLU, bool WIDE>
+// the main loop of the next.  The token rows come through one of four tensor maps
+// with boxes of 64, 128, 192 or 256 rows: the smallest that holds the tile.
+template <int MODE>
 __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w,
-                                                          const __grid_constant__ CUtensorMap tm_x,
+                                                          const __grid_constant__ CUtensorMap tm_x0,
+                                                          const __grid_constant__ CUtensorMap tm_x1,
+                                                          const __grid_constant__ CUtensorMap tm_x2,
+                                                          const __grid_constant__ CUtensorMap tm_x3,
                                                           TcArgs a) {
-  static_assert(!(GLU && WIDE), "gate and up accumulators of a 256-token tile would fill all of TMEM");
-  // a stage holds KSUB 64-wide k-blocks: one with GLU (two weight boxes per
-  // k-block already), two without, so that every stage moves 40-48 KB and the
-  // per-stage barrier round trip is paid half as often on the down projection
+  constexpr bool GLU2 = MODE == TC_GLU2, GLU = GLU2;
+  constexpr bool WIDE = MODE == TC_WIDE;
+  // a stage holds KSUB 64-wide k-blocks: one with two weight boxes per k-block or wide
+  // token boxes, two otherwise, so that every stage moves 40-48 KB and the per-stage
+  // barrier round trip is paid half as often on the narrow down projection
   constexpr int TC_B_BYTES = (WIDE ? 2 : 1) * TC_MAXN * TC_BK * 2;   // reserved per k-block
-  constexpr int KSUB = (GLU || WIDE) ? 1 : 2;
-  constexpr int NA = GLU ? 2 : 1;                     // weight boxes per k-block
-  constexpr int STAGES = (GLU || WIDE) ? 4 : 3;
+  constexpr int KSUB = MODE == TC_PLAIN ? 2 : 1;
+  constexpr int NA = GLU2 ? 2 : 1;                    // 16 KB weight regions per k-block
+  constexpr int STAGES = MODE == TC_PLAIN ? 3 : 4;
   constexpr int STAGE_BYTES = KSUB * (NA * TC_A_BYTES + TC_B_BYTES);
+  constexpr int FEAT = TC_BM;                         // output features per tile
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
@@ -95,7 +122,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ntok = a.ntok;
-  const int acc_cols = GLU ? 2 * ntok : ntok;             // columns of one accumulator buffer
+  const int acc_cols = GLU2 ? 2 * ntok : ntok;            // columns of one accumulator buffer
   const unsigned tmem_cols = 2 * acc_cols <= 32 ? 32u : (2 * acc_cols <= 64 ? 64u :
                              (2 * acc_cols <= 128 ? 128u : (2 * acc_cols <= 256 ? 256u : 512u)));
   if (threadIdx.x == 0) {
@@ -114,19 +141,27 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
   tc_fence_after();
   const unsigned tmem_base = tmem_slot;
   const int kblocks = (a.K + KSUB * TC_BK - 1) / (KSUB * TC_BK);
-  const int wtiles = (a.n_out + TC_BM - 1) / TC_BM;
+  const int wtiles = (a.n_out + FEAT - 1) / FEAT;
   const int total = a.tiles_y * wtiles;
+  // rows (rounded up to 16) the MMA of tile y covers
+  auto tile_n = [&](int e, int row0) {
+    const int begin = a.group_offsets[e], end = a.group_offsets[e + 1];
+    return min(tc_tile_rows(end - begin, ntok), (end - row0 + 15) & ~15);
+  };
 
   if (warp == 0) {
     if (lane == 0) {
-      const unsigned tx = KSUB * (NA * TC_A_BYTES + (unsigned)ntok * TC_BK * 2);
       long long issued = 0;           // k-blocks issued so far, over all tiles
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        const int y = t / wtiles, n0 = (t % wtiles) * TC_BM;
+        const int y = t / wtiles, n0 = (t % wtiles) * FEAT;
         const int e = a.tile_expert[y];
         if (e < 0) continue;
         const int row0 = a.tile_row0[y];
+        // the token box: the smallest of 64 / 128 / 192 / 256 rows that holds the tile
+        const int bucket = (tile_n(e, row0) + 63) / 64 - 1;
+        const CUtensorMap* tm_x = bucket == 0 ? &tm_x0 : (bucket == 1 ? &tm_x1 : (bucket == 2 ? &tm_x2 : &tm_x3));
+        const unsigned tx = KSUB * (NA * TC_A_BYTES + (unsigned)(bucket + 1) * 64 * TC_BK * 2);
         for (int kb = 0; kb < kblocks; ++kb, ++issued) {
           const int s = (int)(issued % STAGES);
           const unsigned ph = (unsigned)(issued / STAGES) & 1u;
@@ -143,8 +178,8 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
             unsigned char* st = tiles + (size_t)s * STAGE_BYTES + sub * (NA * TC_A_BYTES + TC_B_BYTES);
             const int k = (kb * KSUB + sub) * TC_BK;
             tma_load_3d(st, &tm_w, k, n0, e, &full_bar[s]);
-            if (GLU) tma_load_3d(st + TC_A_BYTES, &tm_w, k, a.n_out + n0, e, &full_bar[s]);
-            tma_load_2d(st + NA * TC_A_BYTES, &tm_x, k, row0, &full_bar[s]);
+            if (GLU2) tma_load_3d(st + TC_A_BYTES, &tm_w, k, a.n_out + n0, e, &full_bar[s]);
+            tma_load_2d(st + NA * TC_A_BYTES, tm_x, k, row0, &full_bar[s]);
           }
         }
       }
@@ -167,9 +202,8 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
         const int e = a.tile_expert[y];
         if (e < 0) continue;
         // instruction descriptor: D f32, A/B bf16, both K-major, M = 128, N = the rows
-        // this tile really has, rounded up to 16: an expert's last tile costs what it holds
-        const int left = a.group_offsets[e + 1] - a.tile_row0[y];
-        const int n_tile = min(ntok, (left + 15) & ~15);
+        // this tile really has, rounded up to 16: a tile costs what it holds
+        const int n_tile = tile_n(e, a.tile_row0[y]);
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n_tile >> 3) << 17) |
                                ((unsigned)(TC_BM >> 4) << 24);
         const int b = local & 1;
@@ -199,7 +233,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
               const unsigned acc = (kb | sub | kk) != 0;
               const unsigned long long bdesc = sw128_desc(sb + kk * 32);
               tc_mma(tmem_d, sw128_desc(st + kk * 32), bdesc, idesc, acc);
-              if (GLU) tc_mma(tmem_d + ntok, sw128_desc(st + TC_A_BYTES + kk * 32), bdesc, idesc, acc);
+              if (GLU2) tc_mma(tmem_d + ntok, sw128_desc(st + TC_A_BYTES + kk * 32), bdesc, idesc, acc);
             }
           }
           tc_commit(&empty_bar[s]);
@@ -218,9 +252,8 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
       const int e = a.tile_expert[y];
       if (e < 0) continue;
       const int row0 = a.tile_row0[y], row_end = a.group_offsets[e + 1];
-      const int n = (t % wtiles) * TC_BM + lane_base + lane;
       const int b = local & 1;
-      const int n_tile = min(ntok, (row_end - row0 + 15) & ~15);
+      const int n_tile = tile_n(e, row0);
       // Without GLU (the down projection) a column's output row and route weight come
       // from two dependent loads from global memory: they are fetched for the whole
       // tile before the wait on the accumulator, so that this tile's main loop hides
@@ -247,7 +280,8 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const unsigned tmem_d = tmem_base + (unsigned)(b * acc_cols) + ((unsigned)lane_base << 16);
-      if (GLU) {
+      if (GLU2) {
+        const int n = (t % wtiles) * TC_BM + lane_base + lane;
         for (int c0 = 0; c0 < n_tile; c0 += 16) {
           unsigned g[16], u[16];
           tc_ld16(tmem_d + (unsigned)c0, g);
@@ -265,6 +299,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
           }
         }
       } else {
+        const int n = (t % wtiles) * TC_BM + lane_base + lane;
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
 #pragma unroll
@@ -311,11 +346,13 @@ __global__ void moe_tile_map_kernel(const int* __restrict__ group_offsets, const
   __syncthreads();
   for (int base = 0; base < busy; base += blockDim.x) {
     const int j = base + threadIdx.x;
-    int e = -1, begin = 0, nt = 0;
+    int e = -1, begin = 0, nt = 0, sz = ntok;
     if (j < busy) {
       e = active[j];
       begin = group_offsets[e];
-      nt = (group_offsets[e + 1] - begin + ntok - 1) / ntok;
+      const int r = group_offsets[e + 1] - begin;
+      nt = (r + ntok - 1) / ntok;
+      sz = tc_tile_rows(r, ntok);        // the group's rows dealt out evenly over its tiles
     }
     scan[threadIdx.x] = nt;
     __syncthreads();
@@ -329,7 +366,7 @@ __global__ void moe_tile_map_kernel(const int* __restrict__ group_offsets, const
     const int first = carry + scan[threadIdx.x] - nt;
     for (int i = 0; i < nt && first + i < bound; ++i) {
       tile_expert[first + i] = e;
-      tile_row0[first + i] = begin + i * ntok;
+      tile_row0[first + i] = begin + i * sz;
     }
     __syncthreads();
     if (threadIdx.x == blockDim.x - 1) carry += scan[threadIdx.x];
@@ -372,6 +409,19 @@ static EncodeTiledFn encode_fn() {
       fn = (EncodeTiledFn)p;
   }
   return fn;
+}
+
+template <int MODE>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap* mx, const TcArgs& a, dim3 grid, size_t smem,
+                     cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  moe_gemm_tc_kernel<MODE><<<grid, 192, smem, stream>>>(mw, mx[0], mx[1], mx[2], mx[3], a);
+  return FT_OK;
 }
 
 }  // namespace ft
@@ -441,7 +491,10 @@ int ft_moe_tile_map(const int* group_offsets, const int* active, int* tile_exper
   return FT_OK;
 }
 
-int ft_moe_gemm_tc(const void* map_w, const void* map_x, void* C, long long ldc,
+// `map_w`: the 3-D map of the expert weights with boxes of 128 rows.  `maps_x`: four 2-D
+// maps of the sorted token rows, 128 bytes each, with boxes of 64, 128, 192 and 256 rows.
+// `ntok`: most rows of a token tile (a multiple of 16; up to 128 with GLU, else up to 256).
+int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc,
                    const int* group_offsets, const int* active, const int* tile_expert,
                    const int* tile_row0, const int* c_rows,
                    const float* row_scale, int* status, int rows_bound, int n_out, int K, int G,
@@ -449,9 +502,9 @@ int ft_moe_gemm_tc(const void* map_w, const void* map_x, void* C, long long ldc,
                    cudaStream_t stream) {
   if (rows_bound <= 0 || n_out <= 0) return FT_OK;
   if (ntok < 16 || ntok > (glu ? TC_MAXN : 2 * TC_MAXN) || (ntok & 15) || (K & 7) || G <= 0) return FT_ERR_SHAPE;
-  CUtensorMap mw, mx;
+  CUtensorMap mw, mx[4];
   memcpy(&mw, map_w, sizeof(mw));
-  memcpy(&mx, map_x, sizeof(mx));
+  memcpy(mx, maps_x, sizeof(mx));
   const int tiles_y = ft_tc_tiles_bound(rows_bound, G, ntok);
   TcArgs a{C, group_offsets, active, tile_expert, tile_row0, c_rows, row_scale, status, ldc, n_out, K, G, ntok,
            tiles_y, act, act_alpha, act_limit};
@@ -464,34 +517,11 @@ int ft_moe_gemm_tc(const void* map_w, const void* map_x, void* C, long long ldc,
   const int total = tiles_y * ((n_out + TC_BM - 1) / TC_BM);
   dim3 grid(total < sms ? total : sms);
   constexpr int B_BYTES = TC_MAXN * TC_BK * 2;
-  if (glu) {
-    const size_t smem = 4 * (2 * TC_A_BYTES + B_BYTES) + 1024;
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-      configured = true;
-    }
-    moe_gemm_tc_kernel<true, false><<<grid, 192, smem, stream>>>(mw, mx, a);
-  } else if (ntok > TC_MAXN) {
-    const size_t smem = 4 * (TC_A_BYTES + 2 * B_BYTES) + 1024;
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-      configured = true;
-    }
-    moe_gemm_tc_kernel<false, true><<<grid, 192, smem, stream>>>(mw, mx, a);
-  } else {
-    const size_t smem = 3 * 2 * (TC_A_BYTES + B_BYTES) + 1024;
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-      configured = true;
-    }
-    moe_gemm_tc_kernel<false, false><<<grid, 192, smem, stream>>>(mw, mx, a);
-  }
+  int rc;
+  if (glu) rc = launch_tc<TC_GLU2>(mw, mx, a, grid, 4 * (2 * TC_A_BYTES + B_BYTES) + 1024, stream);
+  else if (ntok > TC_MAXN) rc = launch_tc<TC_WIDE>(mw, mx, a, grid, 4 * (TC_A_BYTES + 2 * B_BYTES) + 1024, stream);
+  else rc = launch_tc<TC_PLAIN>(mw, mx, a, grid, 3 * 2 * (TC_A_BYTES + B_BYTES) + 1024, stream);
+  if (rc != FT_OK) return rc;
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

@@ -382,14 +382,21 @@ def moe_gemm_tc_takes(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool
             and c.stride(1) == 1)
 
 
+# From this many sorted rows per expert (on average) the down projection of the grouped
+# GEMM takes token tiles of up to 256 rows (measured with 64 experts of real width: at 64
+# rows per expert 122 against 115 us, at 128 rows 134 against 138, at 512 rows 379 against
+# 402).  gate_up + GLU keeps two accumulators of up to 128 tokens: all of TMEM otherwise.
+TC_WIDE_FROM_ROWS = int(os.environ.get("FREETOKEN_TC_WIDE_FROM_ROWS", "96"))
+
+
 def tc_tokens_per_tile(rows: int, groups: int, wide: bool = False) -> int:
     """Most tokens of an MMA tile for ``rows`` sorted rows over ``groups`` experts.
-    A tile's product is as wide as the rows it really holds (rounded up to 16), so
-    a large tile costs nothing extra and saves fetching an expert's weights once
-    more for a few rows beyond a small tile: 128, or - for a product without GLU
-    (``wide``) when that lets most experts fit one tile - 256."""
+    A tile's product is as wide as the rows it really holds (rounded up to 16) and an
+    expert's rows are dealt out evenly over its tiles, so a large limit costs nothing
+    extra: 256 when experts are busy (``wide`` says the caller's kernel takes that),
+    else 128."""
     avg = -(-rows // max(1, groups))
-    if wide and 104 <= avg <= 208:
+    if wide and avg >= TC_WIDE_FROM_ROWS:
         return 256
     return 128
 
@@ -416,7 +423,7 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
     """Grouped expert GEMM on tcgen05/TMEM fed by TMA.  ``x`` holds the sorted
     rows ``[>= rows, K]`` (already gathered), ``w`` is ``[G, N_w, K]``; same
     output conventions as :func:`gemm_rows`.  ``tile_map`` comes from
-    :func:`moe_tile_map` with the same ``tokens_per_tile``."""
+    :func:`moe_tile_map` with the same ``tokens_per_tile`` (at most 128 with GLU, else 256)."""
     if not moe_gemm_tc_takes(x, w, c):
         raise KernelError("moe_gemm_tc: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
     G, NW, K = w.shape
@@ -427,10 +434,12 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
         _need(t, name, torch.int32)
     ntok = tokens_per_tile or tc_tokens_per_tile(rows, G)
     map_w = _tc_map(w, NW, K, K, G, 128)
-    map_x = _tc_map(x, x.shape[0], K, x.stride(0), 0, ntok)      # 0: a 2-D map (token rows)
+    # the token rows through boxes of 64, 128, 192 and 256 rows: a tile takes the smallest that holds it
+    maps_x = b"".join(bytes(_tc_map(x, x.shape[0], K, x.stride(0), 0, box)) for box in (64, 128, 192, 256))
+    maps_x = ctypes.create_string_buffer(maps_x, 512)
     status = tc_status(x.device)
     f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p p p i i i i i i i f f")
-    _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(map_x, ctypes.c_void_p), _ptr(c),
+    _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(maps_x, ctypes.c_void_p), _ptr(c),
              c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map[0]), _ptr(tile_map[1]),
              _ptr(c_rows), _ptr(row_scale),
              _ptr(status), rows, N, K, G, ntok, int(glu), 0 if act == "silu" else 1,

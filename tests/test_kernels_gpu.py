@@ -207,18 +207,11 @@ def test_expert_gemms(kernel, E, k, T, H, I, act):
     active = torch.cat([busy, torch.zeros(E - busy.numel(), dtype=torch.int32, device=DEV),
                         torch.tensor([busy.numel()], dtype=torch.int32, device=DEV)])
     if kernel == "tc":
-        xs = torch.empty(R, H, dtype=dt, device=DEV)
-        o.gather_rows(x, sorted_token, xs)
         from freetoken_b200.parts.base import Workspace
-        ntok = o.tc_tokens_per_tile(R, E)
-        tiles = o.moe_tile_map(offsets, active, R, E, ntok, Workspace(DEV))
-        o.moe_gemm_tc(xs, w1, mid, group_offsets=offsets, active=active, tile_map=tiles, rows=R,
-                      glu=True, act=act, tokens_per_tile=ntok)
-        ntok2 = o.tc_tokens_per_tile(R, E, wide=True)
-        if ntok2 != ntok:
-            tiles = o.moe_tile_map(offsets, active, R, E, ntok2, Workspace(DEV), tag=".wide")
-        o.moe_gemm_tc(mid, w2, parts, group_offsets=offsets, active=active, tile_map=tiles,
-                      c_rows=sorted_route, row_scale=rw, rows=R, tokens_per_tile=ntok2)
+        # few rows per expert: 128 features a tile, gate and up as two accumulators; many:
+        # tiles of up to 256 tokens, gate and up rows side by side in one accumulator
+        o.moe_experts_tc(x, w1, w2, mid, parts, offsets, active, sorted_route, sorted_token, rw, R, act,
+                         1.702, 7.0, Workspace(DEV))
         torch.cuda.synchronize()
         o.check_tc_status(DEV)
     elif kernel == "skinny":
