@@ -68,6 +68,7 @@ class EngineArgs:
     max_step_tokens: int = 8192
     cuda_graph_max_bs: int = 64              # decode-only steps up to this batch are graph-replayed; 0: never
     poison_freed_pages: bool = False         # debugging: pages given back are filled with NaN
+    nvtx: bool = False                       # NVTX ranges around every part of every layer (profiling)
 
 
 def _align4(n: int) -> int:
@@ -90,7 +91,7 @@ class Engine:
         if free_before is None:
             free_before = torch.cuda.mem_get_info(self.device)[0]
         self.plan = arch.build_plan(config)
-        self.model = Model(self.plan)
+        self.model = Model(self.plan, nvtx=args.nvtx)
         build.ensure_built(self.model.libraries(self.dtype))
         if self.dtype == torch.bfloat16:
             # asked once, here, so that no step (or graph capture) has to find out

@@ -21,6 +21,7 @@ import torch
 from .csrc import ops
 from .engine.engine import Engine, EngineArgs, StepEntry
 from .engine.scheduler import PlannedEntry, Request, Scheduler
+from .engine.status import StatusReporter
 from .sampling.params import SamplingParams
 from .sampling.sampler import RequestRng, Sampler
 
@@ -67,16 +68,20 @@ class LLM:
                  memory_ratio: float = 0.9, use_dummy_weight: bool = False,
                  cuda_graph_max_bs: int = 64, seed: int = 0,
                  device: str = "cuda:0", config: Optional[Dict[str, Any]] = None,
-                 dummy_weight_options=None):
+                 dummy_weight_options=None, log_status=None, decode_log_interval: int = 40,
+                 nvtx: bool = False):
         """``model_path``: a folder with ``config.json`` and safetensors files.
         With ``use_dummy_weight`` only ``config.json`` (or ``config``) is
         needed and weights are random from ``seed`` (scales from
-        ``dummy_weight_options``, a :class:`freetoken_b200.weights.RandomOptions`)."""
+        ``dummy_weight_options``, a :class:`freetoken_b200.weights.RandomOptions`).
+        ``log_status``: a function that takes a line of text; it receives the scheduler's
+        throughput lines (one per step with prompt tokens, one per
+        ``decode_log_interval`` decode steps).  ``nvtx``: NVTX ranges around every part."""
         args = EngineArgs(dtype=dtype, device=device, page_size=page_size,
                           num_pages=num_page_override, max_tokens=num_token_override,
                           max_running_requests=max_running_req, max_seq_len=max_seq_len_override,
                           memory_ratio=memory_ratio, max_step_tokens=max_extend_tokens,
-                          cuda_graph_max_bs=cuda_graph_max_bs)
+                          cuda_graph_max_bs=cuda_graph_max_bs, nvtx=nvtx)
         raw: Dict[str, Any]
         if config is not None:
             raw = dict(config)
@@ -103,6 +108,7 @@ class LLM:
         self._tok_host: List[Optional[torch.Tensor]] = [None, None]
         self._status_host = [torch.zeros(1, dtype=torch.int32).pin_memory() for _ in range(2)]
         self.d2h_bytes_last_step = 0
+        self.status = StatusReporter(log_status, decode_log_interval=decode_log_interval) if log_status else None
 
     # ---- text ------------------------------------------------------------
     def _tokenizer(self):
@@ -196,6 +202,11 @@ class LLM:
         plan = self.scheduler.plan()
         if not plan:
             return None
+        if self.status is not None:
+            cache = self.engine.cache
+            total, free = sum(cache.total_pages()), sum(cache.free_pages())
+            self.status.report(plan, running=len(self.scheduler.running), queued=len(self.scheduler.pending),
+                               pages_used=total - free, pages_total=total, page_size=cache.page_size)
         prev = self._inflight
         entries = []
         for e in plan:

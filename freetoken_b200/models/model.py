@@ -25,8 +25,22 @@ def _prefix(spec: PartSpec, default: str) -> str:
     return spec.params.get("prefix", default)
 
 
+def _with_nvtx_range(part: Part, name: str) -> None:
+    """Wrap ``part.forward`` in an NVTX range called ``name`` (the reference
+    annotates its layers and ops the same way, python/freetoken/utils/torch_utils.py:23-37)."""
+    inner = part.forward
+
+    def forward(*args, **kwargs):
+        torch.cuda.nvtx.range_push(name)
+        try:
+            return inner(*args, **kwargs)
+        finally:
+            torch.cuda.nvtx.range_pop()
+    part.forward = forward
+
+
 class Model:
-    def __init__(self, plan: ModelPlan):
+    def __init__(self, plan: ModelPlan, nvtx: bool = False):
         plan.validate()
         self.plan = plan
         self.embedding = EMBEDDINGS.get(plan.embedding.kind)(plan.embedding, _prefix(plan.embedding, ""))
@@ -44,6 +58,13 @@ class Model:
             self.blocks.append(block_cls(layer.block, layer.prefix, mixer, ffn, norms))
         self.final_norm = NORMS.get(plan.final_norm.kind)(plan.final_norm, _prefix(plan.final_norm, ""))
         self.head = HEADS.get(plan.head.kind)(plan.head, _prefix(plan.head, ""))
+        if nvtx:
+            for i, block in enumerate(self.blocks):
+                _with_nvtx_range(block, f"layer_{i}")
+                for child in block.children():
+                    _with_nvtx_range(child, f"layer_{i}.{type(child).__name__}")
+            for part, name in ((self.embedding, "embedding"), (self.final_norm, "final_norm"), (self.head, "head")):
+                _with_nvtx_range(part, name)
 
     # ---- weights ---------------------------------------------------------
     def parts(self):

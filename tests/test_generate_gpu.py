@@ -207,3 +207,27 @@ def test_overlapped_scheduling_gives_the_same_tokens(folder_c, dtype, monkeypatc
                for i in range(len(prompts))]
     sync3, over3, _ = both(sampled)
     assert [r["token_ids"] for r in sync3] == [r["token_ids"] for r in over3]
+
+
+def test_status_lines_nvtx_ranges_and_the_default_pool(folder_a):
+    """The scheduler's throughput lines reach the caller's log function, NVTX ranges
+    change no token, and an engine that is given no pool size takes one from the free
+    memory: enough pages for every running request at the longest sequence, no more."""
+    from freetoken_b200 import LLM, SamplingParams
+    vocab = tiny.TINY_A["vocab_size"]
+    prompts = [tiny.tokens(s, n, vocab) for s, n in ((1, 5), (2, 19))]
+    params = SamplingParams(max_tokens=9, ignore_eos=True)
+    lines = []
+    plain = LLM(folder_a, "float32", page_size=4, num_token_override=128, max_running_req=2,
+                max_extend_tokens=8).generate(prompts, params)
+    llm = LLM(folder_a, "float32", page_size=4, max_running_req=2, max_extend_tokens=8,
+              log_status=lines.append, decode_log_interval=2, nvtx=True)
+    out = llm.generate(prompts, params)
+    assert [r["token_ids"] for r in out] == [r["token_ids"] for r in plain]
+    assert sum(l.startswith("Prefill batch, #new-seq:") for l in lines) >= 3      # 24 prompt tokens, 8 a step
+    assert any(l.startswith("Decode batch, #running-req:") for l in lines)
+    cache = llm.engine.cache
+    per_request = -(-tiny.TINY_A["max_position_embeddings"] // 4)
+    assert cache.total_pages() == [2 * per_request]
+    assert llm.engine.max_seq_len == tiny.TINY_A["max_position_embeddings"]
+    assert cache.free_pages() == cache.total_pages()

@@ -254,3 +254,23 @@ def test_planning_one_step_ahead_gives_the_same_outputs_as_the_synchronous_loop(
         return {r.id: (tuple(r.output), r.finish_reason) for r in reqs}
 
     assert run(ahead=True) == run(ahead=False)
+
+
+def test_status_lines_follow_the_reference_wording():
+    """One line per step with prompt tokens, one per N decode-only steps."""
+    from freetoken_b200.engine.scheduler import PlannedEntry
+    from freetoken_b200.engine.status import StatusReporter
+    lines, now = [], [0.0]
+    rep = StatusReporter(lines.append, clock=lambda: now[0], decode_log_interval=3)
+    r = Request("a", [1, 2, 3], SamplingParams(max_tokens=4))
+    now[0] = 0.5
+    rep.report([PlannedEntry(r, [1, 2, 3], True)], running=0, queued=2, pages_used=1, pages_total=4, page_size=16)
+    assert lines == ["Prefill batch, #new-seq: 1, #new-token: 3, #cached-token: 0, token usage: 0.25, "
+                     "#running-req: 0, #queue-req: 2, input throughput (token/s): 6.00"]
+    for step in range(3):
+        now[0] += 1.0
+        rep.report([PlannedEntry(r, [7], True)], running=1, queued=0, pages_used=2, pages_total=4, page_size=16)
+    assert len(lines) == 2
+    # 1 token sampled by the prompt's last portion + 3 decoded, over the 3.5 s since the reporter began
+    assert lines[1] == ("Decode batch, #running-req: 1, #token: 32, token usage: 0.50, "
+                        "gen throughput (token/s): 1.14, #queue-req: 0")
