@@ -435,8 +435,11 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
     ntok = tokens_per_tile or tc_tokens_per_tile(rows, G)
     map_w = _tc_map(w, NW, K, K, G, 128)
     # the token rows through boxes of 64, 128, 192 and 256 rows: a tile takes the smallest that holds it
-    maps_x = b"".join(bytes(_tc_map(x, x.shape[0], K, x.stride(0), 0, box)) for box in (64, 128, 192, 256))
-    maps_x = ctypes.create_string_buffer(maps_x, 512)
+    key = ("x4", x.data_ptr(), x.shape[0], K, x.stride(0))
+    maps_x = _TC_MAPS.get(key)
+    if maps_x is None:
+        joined = b"".join(bytes(_tc_map(x, x.shape[0], K, x.stride(0), 0, box)) for box in (64, 128, 192, 256))
+        maps_x = _TC_MAPS[key] = ctypes.create_string_buffer(joined, 512)
     status = tc_status(x.device)
     f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p p p i i i i i i i f f")
     _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(maps_x, ctypes.c_void_p), _ptr(c),

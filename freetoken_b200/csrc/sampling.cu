@@ -170,12 +170,16 @@ extern "C" int ft_sample(const float* logits, const float* temperature, const in
 // See sampling_static.h.  The scratch lives in the library image; host code
 // only ever sees the symbol as a handle, so the device address is looked up
 // once per device (with that device current) and handed to the kernel.
+#include <mutex>
+
 #include "sampling_static.h"
 
 static __device__ __align__(256) float ft_sample_static_scratch[FT_SAMPLE_STATIC_FLOATS];
 
 static float* ft_sample_static_address(int* error) {
   static float* address[64] = {nullptr};
+  static std::mutex guard;            // two host threads may make their first call at once
+  std::lock_guard<std::mutex> hold(guard);
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) { *error = (int)e; return nullptr; }
