@@ -14,7 +14,7 @@ from plain_model import PlainModel
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 9, 17, 70], "B": [1, 6, 13, 31, 80], "C": [3, 40, 66, 90, 21], "D": [2, 35, 77],
-           "E": [2, 140, 300, 70]}
+           "E": [2, 140, 300, 70], "F": [4, 50, 27]}
 
 
 @pytest.fixture(scope="module")
@@ -95,7 +95,7 @@ CUTS = {"whole": rd.whole, "decode_tail": rd.decode_tail, "portions": rd.portion
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "D", "F"])
 @pytest.mark.parametrize("cut", list(CUTS))
 def test_cut_matches_plain(models, expected, which, dtype, cut):
     reqs = requests_of(which)

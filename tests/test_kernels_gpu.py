@@ -332,7 +332,8 @@ def test_attn_paged_simt(dtype, nq, nkv, d, P, lens, window, standout):
 # ------------------------------------------------------------------ router
 @pytest.mark.parametrize("E,k,softmax,renorm,use_bias,scale", [
     (4, 2, False, True, True, 1.0), (8, 3, True, False, False, 1.5), (256, 8, False, True, True, 2.0),
-    (37, 5, True, True, False, 1.0), (5, 5, False, True, True, 1.0)])
+    (37, 5, True, True, False, 1.0), (5, 5, False, True, True, 1.0),
+    (64, 40, False, True, True, 1.0), (100, 33, True, False, False, 2.0)])       # more choices than a warp has lanes
 def test_router_select(E, k, softmax, renorm, use_bias, scale):
     T = 33
     logits = rnd(T, E, seed=1)

@@ -71,9 +71,22 @@ TINY_E: Dict = dict(
     routed_scaling_factor=1.0, hidden_act="silu", vocab_size=320, tie_word_embeddings=False,
 )
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
-PAGE = {"A": 4, "B": 8, "C": 16, "D": 32, "E": 64}
+# Sizes between the kernels' fast shapes: a head size of 80 (a step of 16 that no
+# tensor-core kernel takes), seven query heads per KV head, 40 of 48 experts per token
+# (more choices than a warp has lanes), a page of 12 tokens.
+TINY_F: Dict = dict(
+    architectures=["MiniMaxM3ForCausalLM"], model_type="minimax_m3",
+    hidden_size=112, num_hidden_layers=2, num_attention_heads=7, num_key_value_heads=1,
+    head_dim=80, rotary_dim=48, rope_theta=25000.0, max_position_embeddings=256,
+    rms_norm_eps=2e-6, use_gemma_norm=True, use_qk_norm=True, qk_norm_type="per_layer",
+    num_local_experts=48, num_experts_per_tok=40, intermediate_size=24,
+    scoring_func="sigmoid", use_routing_bias=True, norm_topk_prob=True,
+    routed_scaling_factor=1.25, hidden_act="swigluoai", vocab_size=211, tie_word_embeddings=False,
+)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 5}
+PAGE = {"A": 4, "B": 8, "C": 16, "D": 32, "E": 64, "F": 12}
 
 
 def random_options(which: str):
@@ -84,6 +97,8 @@ def random_options(which: str):
         return RandomOptions(norm_std=0.1)
     if which in ("D", "E"):
         return RandomOptions(norm_std=0.1)
+    if which == "F":
+        return RandomOptions(norm_std=0.05, router_bias_std=0.2)
     return RandomOptions(norm_std=0.05, router_bias_std=0.05)
 
 
