@@ -82,12 +82,27 @@ __host__ __device__ __forceinline__ int tc_tile_rows(int r, int ntok) {
 //             is bound by streaming each expert's weights once
 //   TC_PLAIN  no GLU, 128 weight rows x up to 128 tokens, two k-blocks per stage
 //   TC_WIDE   no GLU, 128 weight rows x up to 256 tokens
+//   TC_GLUT   gate_up + GLU with the roles swapped: up to 128 TOKENS are the M operand
+//             (a TMEM lane is a token), 128 gate rows and the 128 up rows of the same
+//             features lie one after the other in shared memory as ONE N operand of 256,
+//             so the accumulator's columns c and c + 128 are gate and up of feature c in
+//             the same lane.  An MMA of N = 256 reads 12 KB of shared memory in 128
+//             cycles where two of N = 128 read 16 KB, the port's limit; a thread's GLU
+//             results are consecutive features of its token and leave as 16-byte stores.
+//             For busy experts (the M tile is always 128 rows).  Measured with 256 experts
+//             of real width, against TC_GLU2: 933 against 929 us at 128 rows per expert,
+//             1,385 against 1,533 us at 256, 2,478 against 2,528 us at 512; with 64 experts
+//             and 512 rows each 619 against 701 us.  Every form moves about 13.2 TB/s from
+//             L2 into shared memory there (48 KB per k-block of a tile): that is the bound.
+//             Running an expert's short last tile weight-major (N as narrow as its rows) in
+//             the same kernel was measured and is slower, not faster: a tile costs its
+//             bytes, not its products.
 // (A variant with gate and up rows side by side in ONE accumulator of up to 256 tokens -
 // an MMA of N = 256 reads less of A per flop from shared memory than two of N = 128 -
 // was built and measured: 642 instead of 392 us at 256 rows per expert; its epilogue,
 // which pairs TMEM lane f with lane f + 64 through shared memory, does not hide under
 // the main loop.)
-enum { TC_GLU2 = 0, TC_PLAIN = 1, TC_WIDE = 2 };
+enum { TC_GLU2 = 0, TC_PLAIN = 1, TC_WIDE = 2, TC_GLUT = 3 };
 
 // Persistent: one CTA per SM walks the tiles t = blockIdx.x, + gridDim.x, ...
 // of the (token tile, weight tile) space, weight tile fastest, so CTAs that run
@@ -102,14 +117,14 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
                                                           const __grid_constant__ CUtensorMap tm_x2,
                                                           const __grid_constant__ CUtensorMap tm_x3,
                                                           TcArgs a) {
-  constexpr bool GLU2 = MODE == TC_GLU2, GLU = GLU2;
+  constexpr bool GLU2 = MODE == TC_GLU2, GLUT = MODE == TC_GLUT, GLU = GLU2 || GLUT;
   constexpr bool WIDE = MODE == TC_WIDE;
   // a stage holds KSUB 64-wide k-blocks: one with two weight boxes per k-block or wide
   // token boxes, two otherwise, so that every stage moves 40-48 KB and the per-stage
   // barrier round trip is paid half as often on the narrow down projection
   constexpr int TC_B_BYTES = (WIDE ? 2 : 1) * TC_MAXN * TC_BK * 2;   // reserved per k-block
   constexpr int KSUB = MODE == TC_PLAIN ? 2 : 1;
-  constexpr int NA = GLU2 ? 2 : 1;                    // 16 KB weight regions per k-block
+  constexpr int NA = GLU ? 2 : 1;                     // 16 KB weight regions per k-block
   constexpr int STAGES = MODE == TC_PLAIN ? 3 : 4;
   constexpr int STAGE_BYTES = KSUB * (NA * TC_A_BYTES + TC_B_BYTES);
   constexpr int FEAT = TC_BM;                         // output features per tile
@@ -122,7 +137,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ntok = a.ntok;
-  const int acc_cols = GLU2 ? 2 * ntok : ntok;            // columns of one accumulator buffer
+  const int acc_cols = GLUT ? 2 * TC_BM : (GLU2 ? 2 * ntok : ntok);   // columns of one accumulator buffer
   const unsigned tmem_cols = 2 * acc_cols <= 32 ? 32u : (2 * acc_cols <= 64 ? 64u :
                              (2 * acc_cols <= 128 ? 128u : (2 * acc_cols <= 256 ? 256u : 512u)));
   if (threadIdx.x == 0) {
@@ -178,7 +193,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
             unsigned char* st = tiles + (size_t)s * STAGE_BYTES + sub * (NA * TC_A_BYTES + TC_B_BYTES);
             const int k = (kb * KSUB + sub) * TC_BK;
             tma_load_3d(st, &tm_w, k, n0, e, &full_bar[s]);
-            if (GLU2) tma_load_3d(st + TC_A_BYTES, &tm_w, k, a.n_out + n0, e, &full_bar[s]);
+            if (GLU) tma_load_3d(st + TC_A_BYTES, &tm_w, k, a.n_out + n0, e, &full_bar[s]);
             tma_load_2d(st + NA * TC_A_BYTES, tm_x, k, row0, &full_bar[s]);
           }
         }
@@ -204,8 +219,9 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
         // instruction descriptor: D f32, A/B bf16, both K-major, M = 128, N = the rows
         // this tile really has, rounded up to 16: a tile costs what it holds
         const int n_tile = tile_n(e, a.tile_row0[y]);
-        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n_tile >> 3) << 17) |
-                               ((unsigned)(TC_BM >> 4) << 24);
+        // (token-major GLU: M = 128 token rows, N = 256 weight rows, whatever the tile holds)
+        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                               ((unsigned)((GLUT ? 2 * TC_BM : n_tile) >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
         const int b = local & 1;
         if (!mbar_wait(&acc_empty[b], ((unsigned)(local >> 1) & 1u) ^ 1u, &gave_up)) {
           atomicCAS(a.status, 0, FT_ST_MOE_MMA_ACC);
@@ -232,6 +248,10 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
             for (int kk = 0; kk < TC_BK / 16; ++kk) {
               const unsigned acc = (kb | sub | kk) != 0;
               const unsigned long long bdesc = sw128_desc(sb + kk * 32);
+              if (GLUT) {                  // A: the token rows; B: gate rows then up rows, 256 in all
+                tc_mma(tmem_d, bdesc, sw128_desc(st + kk * 32), idesc, acc);
+                continue;
+              }
               tc_mma(tmem_d, sw128_desc(st + kk * 32), bdesc, idesc, acc);
               if (GLU2) tc_mma(tmem_d + ntok, sw128_desc(st + TC_A_BYTES + kk * 32), bdesc, idesc, acc);
             }
@@ -280,7 +300,43 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const unsigned tmem_d = tmem_base + (unsigned)(b * acc_cols) + ((unsigned)lane_base << 16);
-      if (GLU2) {
+      if (GLUT) {
+        // TMEM lane = token row of the tile; columns c and c + 128 = gate and up of feature n0 + c
+        const int n0 = (t % wtiles) * TC_BM;
+        const int row = row0 + lane_base + lane;
+        const bool valid = lane_base + lane < n_tile && row < row_end;
+        const int crow = valid ? (a.c_rows ? a.c_rows[row] : row) : 0;
+        const float scale = valid && a.row_scale ? a.row_scale[crow] : 1.f;
+        __nv_bfloat16* dst = C + (size_t)crow * a.ldc + n0;
+        const bool vec = (a.ldc & 7) == 0 && ((uintptr_t)C & 15) == 0;
+        for (int c0 = 0; c0 < TC_BM && n0 + c0 < a.n_out; c0 += 16) {
+          unsigned g[16], u[16];
+          tc_ld16(tmem_d + (unsigned)c0, g);
+          tc_ld16(tmem_d + (unsigned)(TC_BM + c0), u);
+          tc_ld_wait();
+          if (!valid) continue;
+          unsigned packed[8];
+#pragma unroll
+          for (int c = 0; c < 16; c += 2) {
+            const float v0 = scale * tc_glu(__uint_as_float(g[c]), __uint_as_float(u[c]), a.act, a.act_alpha, a.act_limit);
+            const float v1 = scale * tc_glu(__uint_as_float(g[c + 1]), __uint_as_float(u[c + 1]), a.act, a.act_alpha, a.act_limit);
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+            packed[c >> 1] = *reinterpret_cast<const unsigned*>(&h);
+          }
+          if (vec && n0 + c0 + 16 <= a.n_out) {
+            *reinterpret_cast<uint4*>(dst + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              if (n0 + c0 + c < a.n_out) {
+                const unsigned w = packed[c >> 1];
+                const unsigned short bits = (c & 1) ? (unsigned short)(w >> 16) : (unsigned short)(w & 0xffffu);
+                dst[c0 + c] = __ushort_as_bfloat16(bits);
+              }
+          }
+        }
+      } else if (GLU2) {
         const int n = (t % wtiles) * TC_BM + lane_base + lane;
         for (int c0 = 0; c0 < n_tile; c0 += 16) {
           unsigned g[16], u[16];
@@ -494,6 +550,8 @@ int ft_moe_tile_map(const int* group_offsets, const int* active, int* tile_exper
 // `map_w`: the 3-D map of the expert weights with boxes of 128 rows.  `maps_x`: four 2-D
 // maps of the sorted token rows, 128 bytes each, with boxes of 64, 128, 192 and 256 rows.
 // `ntok`: most rows of a token tile (a multiple of 16; up to 128 with GLU, else up to 256).
+// `glu`: 0 none; 1 gate and up as two accumulators, weights as the M operand; 2 tokens as
+// the M operand and gate + up rows as one N operand of 256.
 int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc,
                    const int* group_offsets, const int* active, const int* tile_expert,
                    const int* tile_row0, const int* c_rows,
@@ -501,7 +559,8 @@ int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc
                    int ntok, int glu, int act, float act_alpha, float act_limit,
                    cudaStream_t stream) {
   if (rows_bound <= 0 || n_out <= 0) return FT_OK;
-  if (ntok < 16 || ntok > (glu ? TC_MAXN : 2 * TC_MAXN) || (ntok & 15) || (K & 7) || G <= 0) return FT_ERR_SHAPE;
+  if (ntok < 16 || ntok > (glu ? TC_MAXN : 2 * TC_MAXN) || (ntok & 15) || (K & 7) || G <= 0 || glu < 0 || glu > 2)
+    return FT_ERR_SHAPE;
   CUtensorMap mw, mx[4];
   memcpy(&mw, map_w, sizeof(mw));
   memcpy(mx, maps_x, sizeof(mx));
@@ -518,7 +577,8 @@ int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc
   dim3 grid(total < sms ? total : sms);
   constexpr int B_BYTES = TC_MAXN * TC_BK * 2;
   int rc;
-  if (glu) rc = launch_tc<TC_GLU2>(mw, mx, a, grid, 4 * (2 * TC_A_BYTES + B_BYTES) + 1024, stream);
+  if (glu == 2) rc = launch_tc<TC_GLUT>(mw, mx, a, grid, 4 * (2 * TC_A_BYTES + B_BYTES) + 1024, stream);
+  else if (glu) rc = launch_tc<TC_GLU2>(mw, mx, a, grid, 4 * (2 * TC_A_BYTES + B_BYTES) + 1024, stream);
   else if (ntok > TC_MAXN) rc = launch_tc<TC_WIDE>(mw, mx, a, grid, 4 * (TC_A_BYTES + 2 * B_BYTES) + 1024, stream);
   else rc = launch_tc<TC_PLAIN>(mw, mx, a, grid, 3 * 2 * (TC_A_BYTES + B_BYTES) + 1024, stream);
   if (rc != FT_OK) return rc;

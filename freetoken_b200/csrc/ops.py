@@ -387,6 +387,11 @@ def moe_gemm_tc_takes(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool
 # rows per expert 122 against 115 us, at 128 rows 134 against 138, at 512 rows 379 against
 # 402).  gate_up + GLU keeps two accumulators of up to 128 tokens: all of TMEM otherwise.
 TC_WIDE_FROM_ROWS = int(os.environ.get("FREETOKEN_TC_WIDE_FROM_ROWS", "96"))
+# From this many sorted rows per expert (on average) gate_up + GLU runs token-major: the
+# tokens are the MMA's M operand, gate and up rows one N operand of 256.
+# (measured with 256 experts of real width: level at 128 and 192 rows per expert, 10 %
+# faster at 256, 2 % at 512; 12 % with 64 experts of 512 rows).
+TC_GLU_TOKEN_MAJOR_FROM_ROWS = int(os.environ.get("FREETOKEN_TC_GLU_TOKEN_MAJOR_FROM_ROWS", "224"))
 
 
 def tc_tokens_per_tile(rows: int, groups: int, wide: bool = False) -> int:
@@ -417,13 +422,15 @@ def moe_tile_map(group_offsets: torch.Tensor, active: torch.Tensor, rows: int, g
 
 def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offsets: torch.Tensor,
                 active: torch.Tensor, tile_map: tuple, c_rows: Optional[torch.Tensor] = None,
-                row_scale: Optional[torch.Tensor] = None, rows: int, glu: bool = False,
+                row_scale: Optional[torch.Tensor] = None, rows: int, glu: int = 0,
                 act: str = "silu", act_alpha: float = 1.702, act_limit: float = 7.0,
                 tokens_per_tile: Optional[int] = None) -> None:
     """Grouped expert GEMM on tcgen05/TMEM fed by TMA.  ``x`` holds the sorted
     rows ``[>= rows, K]`` (already gathered), ``w`` is ``[G, N_w, K]``; same
     output conventions as :func:`gemm_rows`.  ``tile_map`` comes from
-    :func:`moe_tile_map` with the same ``tokens_per_tile`` (at most 128 with GLU, else 256)."""
+    :func:`moe_tile_map` with the same ``tokens_per_tile`` (at most 128 with GLU, else 256).
+    ``glu``: 0 none; 1 (or True) gate and up as two accumulators with the weights as the
+    M operand; 2 token-major (tokens the M operand, gate + up rows one N operand of 256)."""
     if not moe_gemm_tc_takes(x, w, c):
         raise KernelError("moe_gemm_tc: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
     G, NW, K = w.shape
@@ -462,9 +469,10 @@ def moe_experts_tc(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tenso
     xs = workspace.get("moe.sorted_x", (rows, x.shape[1]), x.dtype)
     gather_rows(x, sorted_token, xs)
     ntok = tc_tokens_per_tile(rows, G)
+    token_major = -(-rows // max(1, G)) >= TC_GLU_TOKEN_MAJOR_FROM_ROWS
     tiles = moe_tile_map(group_offsets, active, rows, G, ntok, workspace)
     moe_gemm_tc(xs, w_gate_up, mid, group_offsets=group_offsets, active=active, tile_map=tiles,
-                rows=rows, glu=True, act=act, act_alpha=act_alpha, act_limit=act_limit,
+                rows=rows, glu=2 if token_major else 1, act=act, act_alpha=act_alpha, act_limit=act_limit,
                 tokens_per_tile=ntok)
     # the down projection takes wider token tiles when experts are busy enough
     ntok2 = tc_tokens_per_tile(rows, G, wide=True)

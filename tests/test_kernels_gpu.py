@@ -185,15 +185,19 @@ def _grouped_case(E, k, T, seed=0):
     return ids.to(DEV), order.to(DEV), (order // k).to(torch.int32).to(DEV), offsets.to(DEV)
 
 
-@pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "skinny", "tc"])
+@pytest.mark.parametrize("kernel", ["simt_f32", "simt_bf16", "skinny", "tc", "tc_weight_major", "tc_token_major"])
 @pytest.mark.parametrize("E,k,T,H,I,act", [(4, 2, 5, 64, 32, "silu"), (8, 3, 19, 96, 48, "swigluoai"),
+                                           (4, 2, 400, 96, 144, "swigluoai"),  # 200 rows per expert
                                            (16, 4, 150, 128, 80, "silu"), (3, 1, 40, 40, 24, "silu"),
                                            (8, 2, 700, 264, 200, "silu"),
                                            (4, 2, 650, 136, 72, "silu"),      # 325 rows per expert: wide tiles
                                            (1, 1, 300, 128, 80, "silu")])     # a single expert: still a 3-D weight map
-def test_expert_gemms(kernel, E, k, T, H, I, act):
+def test_expert_gemms(kernel, E, k, T, H, I, act, monkeypatch):
     """gate_up + GLU, then down with the route weight, against a per-route loop."""
     o = ops()
+    if kernel.startswith("tc_"):         # force one form of the GLU tile whatever the load
+        monkeypatch.setattr(o, "TC_GLU_TOKEN_MAJOR_FROM_ROWS", 0 if kernel == "tc_token_major" else 1 << 30)
+        kernel = "tc"
     dt = torch.float32 if kernel == "simt_f32" else torch.bfloat16
     x = rnd(T, H, dtype=dt, seed=1)
     w1 = rnd(E, 2 * I, H, dtype=dt, seed=2, scale=0.1)
@@ -208,8 +212,8 @@ def test_expert_gemms(kernel, E, k, T, H, I, act):
                         torch.tensor([busy.numel()], dtype=torch.int32, device=DEV)])
     if kernel == "tc":
         from freetoken_b200.parts.base import Workspace
-        # few rows per expert: 128 features a tile, gate and up as two accumulators; many:
-        # tiles of up to 256 tokens, gate and up rows side by side in one accumulator
+        # few rows per expert: the weights are the M operand, gate and up two accumulators;
+        # many: the tokens are the M operand, gate and up rows one N operand of 256
         o.moe_experts_tc(x, w1, w2, mid, parts, offsets, active, sorted_route, sorted_token, rw, R, act,
                          1.702, 7.0, Workspace(DEV))
         torch.cuda.synchronize()
