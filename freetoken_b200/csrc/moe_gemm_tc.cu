@@ -390,6 +390,232 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
   }
 }
 
+// The down projection on CTA PAIRS (`cta_group::2`): a cluster of two CTAs computes
+//   D[256 weight rows, N tokens] = W_e tile * X^T,   N = 32..256 in steps of 32.
+// CTA r of the pair loads weight rows n0 + 128 r .. + 127 (its half of the M operand)
+// and token rows row0 + r N/2 .. (its half of the N operand) into its own shared memory;
+// the even CTA issues one MMA of M = 256 per 16 k, which reads both halves of the tokens
+// from both CTAs and leaves 128 accumulator rows in each CTA's TMEM.  A k-block moves
+// 16 KB of weights and at most 16 KB of tokens into a CTA where a lone CTA moves 16 + 32.
+//
+//   full[s]       (even CTA's) counts the bytes of BOTH CTAs' loads of stage s
+//   empty[s]      (each CTA's own) the even CTA's commit arrives on both
+//   acc_full[b]   (each CTA's own) likewise
+//   acc_empty[b]  (even CTA's) the four epilogue warps of both CTAs arrive on it
+// The roles are those of the kernel above; the odd CTA's warp 1 only allocates TMEM.
+// Neither CTA leaves before the other is done with its shared memory and barriers: the
+// producers wait for the last commits on their stages, and a cluster barrier precedes
+// the TMEM release.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGE_BYTES = TC_A_BYTES + TC_MAXN * TC_BK * 2;   // 16 KB weights + up to 128 token rows
+
+__global__ void __launch_bounds__(192) moe_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w,
+                                                               const __grid_constant__ CUtensorMap tm_x0,
+                                                               const __grid_constant__ CUtensorMap tm_x1,
+                                                               const __grid_constant__ CUtensorMap tm_x2,
+                                                               const __grid_constant__ CUtensorMap tm_x3,
+                                                               TcArgs a) {
+  constexpr int STAGES = PAIR_STAGES;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
+  __shared__ __align__(8) unsigned long long acc_full[2], acc_empty[2];
+  __shared__ unsigned tmem_slot;
+  __shared__ volatile int gave_up;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned rank = cluster_ctarank();          // 0: the pair's leader
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int ntok = a.ntok;                          // at most 256
+  const unsigned tmem_cols = 512;                   // two accumulators of up to 256 columns
+  if (threadIdx.x == 0) {
+    gave_up = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                 "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    tc_fence_before();
+  }
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();                               // both CTAs' barriers exist before anyone signals them
+  tc_fence_after();
+  const unsigned tmem_base = tmem_slot;
+  const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+  const int wtiles = (a.n_out + 2 * TC_BM - 1) / (2 * TC_BM);
+  const int total = a.tiles_y * wtiles;
+  // rows the pair's MMA covers for tile y: the tile's rows rounded up to 32, so that each
+  // CTA holds a multiple of 16
+  auto tile_n = [&](int e, int row0) {
+    const int begin = a.group_offsets[e], end = a.group_offsets[e + 1];
+    return (min(tc_tile_rows(end - begin, ntok), (end - row0 + 15) & ~15) + 31) & ~31;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      long long issued = 0;
+      bool ok = true;
+      const unsigned leader_full = cluster_addr_of(&full_bar[0], 0);   // + 8 s: the leader's full[s]
+      for (int t = pair; t < total && ok; t += pairs) {
+        const int y = t / wtiles, n0 = (t % wtiles) * 2 * TC_BM + (int)rank * TC_BM;
+        const int e = a.tile_expert[y];
+        if (e < 0) continue;
+        const int half = tile_n(e, a.tile_row0[y]) >> 1;
+        const int row0 = a.tile_row0[y] + (int)rank * half;
+        // the token box: the smallest of 32 / 64 / 96 / 128 rows that holds this CTA's half
+        const int bucket = (half + 31) / 32 - 1;
+        const CUtensorMap* tm_x = bucket == 0 ? &tm_x0 : (bucket == 1 ? &tm_x1 : (bucket == 2 ? &tm_x2 : &tm_x3));
+        const unsigned tx = 2u * (TC_A_BYTES + (unsigned)(bucket + 1) * 32 * TC_BK * 2);   // both CTAs' bytes
+        for (int kb = 0; kb < kblocks; ++kb, ++issued) {
+          const int s = (int)(issued % STAGES);
+          const unsigned ph = (unsigned)(issued / STAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, &gave_up)) {
+            atomicCAS(a.status, 0, FT_ST_MOE_PRODUCER);
+            gave_up = 1;
+            ok = false;
+            break;
+          }
+          if (rank == 0) mbar_expect_tx(&full_bar[s], tx);
+          unsigned char* st = tiles + (size_t)s * PAIR_STAGE_BYTES;
+          const int k = kb * TC_BK;
+          tma_load_3d_pair(st, &tm_w, k, n0, e, leader_full + 8u * (unsigned)s);
+          tma_load_2d_pair(st + TC_A_BYTES, tm_x, k, row0, leader_full + 8u * (unsigned)s);
+        }
+      }
+      // the leader's commits for the last uses of the stages arrive on this CTA's barriers:
+      // stay until they have (and, after a failure, until copies in flight have landed)
+      for (long long kb = issued > STAGES ? issued - STAGES : 0; kb < issued; ++kb) {
+        const int s = (int)(kb % STAGES);
+        const unsigned ph = (unsigned)(kb / STAGES) & 1u;
+        if (!gave_up) {
+          if (!mbar_wait(&empty_bar[s], ph, &gave_up)) {
+            atomicCAS(a.status, 0, FT_ST_MOE_PRODUCER);
+            gave_up = 1;
+          }
+        } else if (rank == 0) {
+          const unsigned long long start = global_ns();
+          while (!mbar_try(&full_bar[s], ph) && global_ns() - start < 100000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      long long done = 0;
+      int local = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += pairs) {
+        const int y = t / wtiles;
+        const int e = a.tile_expert[y];
+        if (e < 0) continue;
+        const int n_tile = tile_n(e, a.tile_row0[y]);
+        // D f32, A/B bf16, both K-major, M = 256 over the pair, N = the tile's rows
+        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n_tile >> 3) << 17) |
+                               ((unsigned)((2 * TC_BM) >> 4) << 24);
+        const int b = local & 1;
+        if (!mbar_wait(&acc_empty[b], ((unsigned)(local >> 1) & 1u) ^ 1u, &gave_up)) {
+          atomicCAS(a.status, 0, FT_ST_MOE_MMA_ACC);
+          gave_up = 1;
+          break;
+        }
+        tc_fence_after();
+        const unsigned tmem_d = tmem_base + (unsigned)(b * ntok);
+        for (int kb = 0; kb < kblocks; ++kb, ++done) {
+          const int s = (int)(done % STAGES);
+          const unsigned ph = (unsigned)(done / STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, &gave_up)) {
+            atomicCAS(a.status, 0, FT_ST_MOE_MMA_STAGE);
+            gave_up = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const unsigned st = smem_u32(tiles + (size_t)s * PAIR_STAGE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < TC_BK / 16; ++kk)
+            tc_mma_pair(tmem_d, sw128_desc(st + kk * 32), sw128_desc(st + TC_A_BYTES + kk * 32), idesc,
+                        (kb | kk) != 0);
+          tc_commit_pair(&empty_bar[s]);
+        }
+        if (ok) tc_commit_pair(&acc_full[b]);
+        ++local;
+      }
+    }
+  } else {
+    // epilogue: TMEM lane = one of this CTA's 128 weight rows
+    const int lane_base = (warp & 3) * 32;
+    __nv_bfloat16* C = (__nv_bfloat16*)a.C;
+    unsigned leader_acc_empty[2];
+    leader_acc_empty[0] = cluster_addr_of(&acc_empty[0], 0);
+    leader_acc_empty[1] = cluster_addr_of(&acc_empty[1], 0);
+    int local = 0;
+    for (int t = pair; t < total; t += pairs) {
+      const int y = t / wtiles;
+      const int e = a.tile_expert[y];
+      if (e < 0) continue;
+      const int row0 = a.tile_row0[y], row_end = a.group_offsets[e + 1];
+      const int b = local & 1;
+      const int n_tile = tile_n(e, row0);
+      // a column's output row and route weight, fetched before the accumulator is waited
+      // for; lane l keeps columns l, l + 32, ...; handed round by shuffle
+      constexpr int NQ = 2 * TC_MAXN / 32;
+      int my_crow[NQ];
+      float my_scale[NQ];
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+        const int row = row0 + q * 32 + lane;
+        my_crow[q] = -1;
+        my_scale[q] = 1.f;
+        if (q * 32 + lane < n_tile && row < row_end) {
+          my_crow[q] = a.c_rows ? a.c_rows[row] : row;
+          if (a.row_scale) my_scale[q] = a.row_scale[my_crow[q]];
+        }
+      }
+      bool ok = mbar_wait(&acc_full[b], (unsigned)(local >> 1) & 1u, &gave_up);
+      if (!ok && lane == 0) { atomicCAS(a.status, 0, FT_ST_MOE_EPILOGUE); gave_up = 1; }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      tc_fence_after();
+      const unsigned tmem_d = tmem_base + (unsigned)(b * ntok) + ((unsigned)lane_base << 16);
+      const int n = (t % wtiles) * 2 * TC_BM + (int)rank * TC_BM + lane_base + lane;
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int c0 = q * 32 + half * 16;
+          if (c0 < n_tile) {
+            unsigned g[16];
+            tc_ld16(tmem_d + (unsigned)c0, g);
+            tc_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int crow = __shfl_sync(0xffffffffu, my_crow[q], half * 16 + c);
+              const float scale = __shfl_sync(0xffffffffu, my_scale[q], half * 16 + c);
+              if (crow >= 0 && n < a.n_out)
+                C[(size_t)crow * a.ldc + n] = __float2bfloat16_rn(__uint_as_float(g[c]) * scale);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_acc_empty[b]);
+      ++local;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
 // tile_expert[y], tile_row0[y] for every (busy expert, tile of ntok rows), in
 // expert order; entries past the last tile get expert -1.  One block.
 __global__ void moe_tile_map_kernel(const int* __restrict__ group_offsets, const int* __restrict__ active,
@@ -582,6 +808,54 @@ int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc
   else if (ntok > TC_MAXN) rc = launch_tc<TC_WIDE>(mw, mx, a, grid, 4 * (TC_A_BYTES + 2 * B_BYTES) + 1024, stream);
   else rc = launch_tc<TC_PLAIN>(mw, mx, a, grid, 3 * 2 * (TC_A_BYTES + B_BYTES) + 1024, stream);
   if (rc != FT_OK) return rc;
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+// The down projection (no GLU) on CTA pairs: `maps_x` holds four 2-D maps of the sorted
+// token rows with boxes of 32, 64, 96 and 128 rows (a CTA loads half of a tile's rows);
+// `ntok` (a multiple of 32, at most 256) and the tile map as for ft_moe_gemm_tc.
+int ft_moe_gemm_tc_pair(const void* map_w, const void* maps_x, void* C, long long ldc,
+                        const int* group_offsets, const int* active, const int* tile_expert,
+                        const int* tile_row0, const int* c_rows, const float* row_scale, int* status,
+                        int rows_bound, int n_out, int K, int G, int ntok, cudaStream_t stream) {
+  if (rows_bound <= 0 || n_out <= 0) return FT_OK;
+  if (ntok < 32 || ntok > 2 * TC_MAXN || (ntok & 31) || (K & 7) || G <= 0) return FT_ERR_SHAPE;
+  CUtensorMap mw, mx[4];
+  memcpy(&mw, map_w, sizeof(mw));
+  memcpy(mx, maps_x, sizeof(mx));
+  const int tiles_y = ft_tc_tiles_bound(rows_bound, G, ntok);
+  TcArgs a{C, group_offsets, active, tile_expert, tile_row0, c_rows, row_scale, status, ldc, n_out, K, G, ntok,
+           tiles_y, 0, 0.f, 0.f};
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int total = tiles_y * ((n_out + 2 * TC_BM - 1) / (2 * TC_BM));
+  const int pairs = total < sms / 2 ? total : sms / 2;
+  const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, moe_gemm_tc_pair_kernel, mw, mx[0], mx[1], mx[2], mx[3], a);
+  if (e != cudaSuccess) return (int)e;
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

@@ -456,6 +456,33 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
              float(act_alpha), float(act_limit), _stream()), "moe_gemm_tc")
 
 
+def moe_gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offsets: torch.Tensor,
+                     active: torch.Tensor, tile_map: tuple, c_rows: Optional[torch.Tensor] = None,
+                     row_scale: Optional[torch.Tensor] = None, rows: int, tokens_per_tile: int = 256) -> None:
+    """The grouped GEMM without GLU on CTA pairs (``cta_group::2``): two CTAs of a cluster
+    share a tile of 256 weight rows by up to 256 tokens, each loading half of both
+    operands.  Same conventions as :func:`moe_gemm_tc`; ``tokens_per_tile`` a multiple of 32."""
+    if not moe_gemm_tc_takes(x, w, c):
+        raise KernelError("moe_gemm_tc_pair: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
+    G, N, K = w.shape
+    if x.shape[1] != K or c.shape[1] != N:
+        raise KernelError("moe_gemm_tc_pair: shapes do not match")
+    for name, t in (("group_offsets", group_offsets), ("active", active)):
+        _need(t, name, torch.int32)
+    map_w = _tc_map(w, N, K, K, G, 128)
+    key = ("x4pair", x.data_ptr(), x.shape[0], K, x.stride(0))
+    maps_x = _TC_MAPS.get(key)
+    if maps_x is None:
+        joined = b"".join(bytes(_tc_map(x, x.shape[0], K, x.stride(0), 0, box)) for box in (32, 64, 96, 128))
+        maps_x = _TC_MAPS[key] = ctypes.create_string_buffer(joined, 512)
+    status = tc_status(x.device)
+    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc_pair", "p p p q p p p p p p p i i i i i")
+    _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(maps_x, ctypes.c_void_p), _ptr(c),
+             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map[0]), _ptr(tile_map[1]),
+             _ptr(c_rows), _ptr(row_scale), _ptr(status), rows, N, K, G, tokens_per_tile, _stream()),
+           "moe_gemm_tc_pair")
+
+
 def moe_experts_tc(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, mid: torch.Tensor,
                    parts: torch.Tensor, group_offsets: torch.Tensor, active: torch.Tensor,
                    sorted_route: torch.Tensor, sorted_token: torch.Tensor, route_weight: torch.Tensor,
