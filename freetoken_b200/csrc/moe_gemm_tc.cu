@@ -45,8 +45,8 @@ struct TcArgs {
   void* C;
   const int* group_offsets;   // [G+1]
   const int* active;          // [G+1]: experts with rows, then their number
-  const int* tile_expert;     // [tiles_bound]: expert of each (expert, token tile), -1 past the end
-  const int* tile_row0;       // [tiles_bound]: first sorted row of the tile
+  const int4* tile_info;      // [tiles_bound]: {expert (-1 past the end), first sorted row, rows the MMA
+                              // covers (rounded up to 16), end of the expert's rows} of each token tile
   const int* c_rows;          // sorted row -> output row, or nullptr
   const float* row_scale;     // by output row, or nullptr
   int* status;                // 0 = fine; otherwise the first failure code
@@ -158,23 +158,22 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
   const int kblocks = (a.K + KSUB * TC_BK - 1) / (KSUB * TC_BK);
   const int wtiles = (a.n_out + FEAT - 1) / FEAT;
   const int total = a.tiles_y * wtiles;
-  // rows (rounded up to 16) the MMA of tile y covers
-  auto tile_n = [&](int e, int row0) {
-    const int begin = a.group_offsets[e], end = a.group_offsets[e + 1];
-    return min(tc_tile_rows(end - begin, ntok), (end - row0 + 15) & ~15);
-  };
+  // A role reads the entry of its NEXT tile while it works on the current one: under load
+  // a load from global memory takes microseconds, and a tile's first copy or product must
+  // not wait for it.  Tiles are in order, so nothing follows an empty entry.
+  auto tile_at = [&](int t) { return t < total ? __ldg(&a.tile_info[t / wtiles]) : make_int4(-1, 0, 0, 0); };
 
   if (warp == 0) {
     if (lane == 0) {
       long long issued = 0;           // k-blocks issued so far, over all tiles
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        const int y = t / wtiles, n0 = (t % wtiles) * FEAT;
-        const int e = a.tile_expert[y];
-        if (e < 0) continue;
-        const int row0 = a.tile_row0[y];
+      int4 cur = tile_at(blockIdx.x);
+      for (int t = blockIdx.x; t < total && ok && cur.x >= 0; t += gridDim.x) {
+        const int4 nxt = tile_at(t + gridDim.x);
+        const int n0 = (t % wtiles) * FEAT;
+        const int e = cur.x, row0 = cur.y;
         // the token box: the smallest of 64 / 128 / 192 / 256 rows that holds the tile
-        const int bucket = (tile_n(e, row0) + 63) / 64 - 1;
+        const int bucket = (cur.z + 63) / 64 - 1;
         const CUtensorMap* tm_x = bucket == 0 ? &tm_x0 : (bucket == 1 ? &tm_x1 : (bucket == 2 ? &tm_x2 : &tm_x3));
         const unsigned tx = KSUB * (NA * TC_A_BYTES + (unsigned)(bucket + 1) * 64 * TC_BK * 2);
         for (int kb = 0; kb < kblocks; ++kb, ++issued) {
@@ -197,6 +196,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
             tma_load_2d(st + NA * TC_A_BYTES, tm_x, k, row0, &full_bar[s]);
           }
         }
+        cur = nxt;
       }
       if (gave_up) {
         // let copies already in flight land before the CTA (and its shared memory) goes away
@@ -212,13 +212,12 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
       long long done = 0;             // k-blocks consumed so far
       int local = 0;                  // tiles this CTA has started
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        const int y = t / wtiles;
-        const int e = a.tile_expert[y];
-        if (e < 0) continue;
+      int4 cur = tile_at(blockIdx.x);
+      for (int t = blockIdx.x; t < total && ok && cur.x >= 0; t += gridDim.x) {
+        const int4 nxt = tile_at(t + gridDim.x);
         // instruction descriptor: D f32, A/B bf16, both K-major, M = 128, N = the rows
         // this tile really has, rounded up to 16: a tile costs what it holds
-        const int n_tile = tile_n(e, a.tile_row0[y]);
+        const int n_tile = cur.z;
         // (token-major GLU: M = 128 token rows, N = 256 weight rows, whatever the tile holds)
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                                ((unsigned)((GLUT ? 2 * TC_BM : n_tile) >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
@@ -260,6 +259,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
         }
         if (ok) tc_commit(&acc_full[b]);
         ++local;
+        cur = nxt;
       }
     }
   } else {
@@ -267,13 +267,12 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
     const int lane_base = (warp & 3) * 32;
     __nv_bfloat16* C = (__nv_bfloat16*)a.C;
     int local = 0;
-    for (int t = blockIdx.x; t < total; t += gridDim.x) {
-      const int y = t / wtiles;
-      const int e = a.tile_expert[y];
-      if (e < 0) continue;
-      const int row0 = a.tile_row0[y], row_end = a.group_offsets[e + 1];
+    int4 cur = tile_at(blockIdx.x);
+    for (int t = blockIdx.x; t < total && cur.x >= 0; t += gridDim.x) {
+      const int4 nxt = tile_at(t + gridDim.x);
+      const int row0 = cur.y, row_end = cur.w;
       const int b = local & 1;
-      const int n_tile = tile_n(e, row0);
+      const int n_tile = cur.z;
       // Without GLU (the down projection) a column's output row and route weight come
       // from two dependent loads from global memory: they are fetched for the whole
       // tile before the wait on the accumulator, so that this tile's main loop hides
@@ -380,6 +379,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[b]);
       ++local;
+      cur = nxt;
     }
   }
   tc_fence_before();
@@ -448,11 +448,12 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_pair_kernel(const __grid_cons
   const int kblocks = (a.K + TC_BK - 1) / TC_BK;
   const int wtiles = (a.n_out + 2 * TC_BM - 1) / (2 * TC_BM);
   const int total = a.tiles_y * wtiles;
-  // rows the pair's MMA covers for tile y: the tile's rows rounded up to 32, so that each
-  // CTA holds a multiple of 16
-  auto tile_n = [&](int e, int row0) {
-    const int begin = a.group_offsets[e], end = a.group_offsets[e + 1];
-    return (min(tc_tile_rows(end - begin, ntok), (end - row0 + 15) & ~15) + 31) & ~31;
+  // (the pair's MMA covers a tile's rows rounded up to 32, so that each CTA holds a multiple
+  // of 16; a role reads the entry of its next tile while it works on the current one)
+  auto tile_at = [&](int t) {
+    int4 ti = t < total ? __ldg(&a.tile_info[t / wtiles]) : make_int4(-1, 0, 0, 0);
+    ti.z = (ti.z + 31) & ~31;
+    return ti;
   };
 
   if (warp == 0) {
@@ -460,12 +461,13 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_pair_kernel(const __grid_cons
       long long issued = 0;
       bool ok = true;
       const unsigned leader_full = cluster_addr_of(&full_bar[0], 0);   // + 8 s: the leader's full[s]
-      for (int t = pair; t < total && ok; t += pairs) {
-        const int y = t / wtiles, n0 = (t % wtiles) * 2 * TC_BM + (int)rank * TC_BM;
-        const int e = a.tile_expert[y];
-        if (e < 0) continue;
-        const int half = tile_n(e, a.tile_row0[y]) >> 1;
-        const int row0 = a.tile_row0[y] + (int)rank * half;
+      int4 cur = tile_at(pair);
+      for (int t = pair; t < total && ok && cur.x >= 0; t += pairs) {
+        const int4 nxt = tile_at(t + pairs);
+        const int n0 = (t % wtiles) * 2 * TC_BM + (int)rank * TC_BM;
+        const int e = cur.x;
+        const int half = cur.z >> 1;
+        const int row0 = cur.y + (int)rank * half;
         // the token box: the smallest of 32 / 64 / 96 / 128 rows that holds this CTA's half
         const int bucket = (half + 31) / 32 - 1;
         const CUtensorMap* tm_x = bucket == 0 ? &tm_x0 : (bucket == 1 ? &tm_x1 : (bucket == 2 ? &tm_x2 : &tm_x3));
@@ -485,6 +487,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_pair_kernel(const __grid_cons
           tma_load_3d_pair(st, &tm_w, k, n0, e, leader_full + 8u * (unsigned)s);
           tma_load_2d_pair(st + TC_A_BYTES, tm_x, k, row0, leader_full + 8u * (unsigned)s);
         }
+        cur = nxt;
       }
       // the leader's commits for the last uses of the stages arrive on this CTA's barriers:
       // stay until they have (and, after a failure, until copies in flight have landed)
@@ -507,11 +510,10 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_pair_kernel(const __grid_cons
       long long done = 0;
       int local = 0;
       bool ok = true;
-      for (int t = pair; t < total && ok; t += pairs) {
-        const int y = t / wtiles;
-        const int e = a.tile_expert[y];
-        if (e < 0) continue;
-        const int n_tile = tile_n(e, a.tile_row0[y]);
+      int4 cur = tile_at(pair);
+      for (int t = pair; t < total && ok && cur.x >= 0; t += pairs) {
+        const int4 nxt = tile_at(t + pairs);
+        const int n_tile = cur.z;
         // D f32, A/B bf16, both K-major, M = 256 over the pair, N = the tile's rows
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n_tile >> 3) << 17) |
                                ((unsigned)((2 * TC_BM) >> 4) << 24);
@@ -542,6 +544,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_pair_kernel(const __grid_cons
         }
         if (ok) tc_commit_pair(&acc_full[b]);
         ++local;
+        cur = nxt;
       }
     }
   } else {
@@ -552,13 +555,12 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_pair_kernel(const __grid_cons
     leader_acc_empty[0] = cluster_addr_of(&acc_empty[0], 0);
     leader_acc_empty[1] = cluster_addr_of(&acc_empty[1], 0);
     int local = 0;
-    for (int t = pair; t < total; t += pairs) {
-      const int y = t / wtiles;
-      const int e = a.tile_expert[y];
-      if (e < 0) continue;
-      const int row0 = a.tile_row0[y], row_end = a.group_offsets[e + 1];
+    int4 cur = tile_at(pair);
+    for (int t = pair; t < total && cur.x >= 0; t += pairs) {
+      const int4 nxt = tile_at(t + pairs);
+      const int row0 = cur.y, row_end = cur.w;
       const int b = local & 1;
-      const int n_tile = tile_n(e, row0);
+      const int n_tile = cur.z;
       // a column's output row and route weight, fetched before the accumulator is waited
       // for; lane l keeps columns l, l + 32, ...; handed round by shuffle
       constexpr int NQ = 2 * TC_MAXN / 32;
@@ -604,6 +606,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_pair_kernel(const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_acc_empty[b]);
       ++local;
+      cur = nxt;
     }
   }
   tc_fence_before();
@@ -616,11 +619,11 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_pair_kernel(const __grid_cons
   }
 }
 
-// tile_expert[y], tile_row0[y] for every (busy expert, tile of ntok rows), in
-// expert order; entries past the last tile get expert -1.  One block.
+// tile_info[y] = {expert, first sorted row, rows the MMA covers (rounded up to 16), end of
+// the expert's rows} for every (busy expert, tile of ntok rows), in expert order; entries
+// past the last tile get expert -1.  One block.
 __global__ void moe_tile_map_kernel(const int* __restrict__ group_offsets, const int* __restrict__ active,
-                                    int* __restrict__ tile_expert, int* __restrict__ tile_row0, int G,
-                                    int ntok, int bound) {
+                                    int4* __restrict__ tile_info, int G, int ntok, int bound) {
   __shared__ int scan[1024];
   __shared__ int carry;
   const int busy = active[G];
@@ -628,11 +631,12 @@ __global__ void moe_tile_map_kernel(const int* __restrict__ group_offsets, const
   __syncthreads();
   for (int base = 0; base < busy; base += blockDim.x) {
     const int j = base + threadIdx.x;
-    int e = -1, begin = 0, nt = 0, sz = ntok;
+    int e = -1, begin = 0, end = 0, nt = 0, sz = ntok;
     if (j < busy) {
       e = active[j];
       begin = group_offsets[e];
-      const int r = group_offsets[e + 1] - begin;
+      end = group_offsets[e + 1];
+      const int r = end - begin;
       nt = (r + ntok - 1) / ntok;
       sz = tc_tile_rows(r, ntok);        // the group's rows dealt out evenly over its tiles
     }
@@ -647,14 +651,14 @@ __global__ void moe_tile_map_kernel(const int* __restrict__ group_offsets, const
     }
     const int first = carry + scan[threadIdx.x] - nt;
     for (int i = 0; i < nt && first + i < bound; ++i) {
-      tile_expert[first + i] = e;
-      tile_row0[first + i] = begin + i * sz;
+      const int row0 = begin + i * sz;
+      tile_info[first + i] = make_int4(e, row0, min(sz, (end - row0 + 15) & ~15), end);
     }
     __syncthreads();
     if (threadIdx.x == blockDim.x - 1) carry += scan[threadIdx.x];
     __syncthreads();
   }
-  for (int i = carry + threadIdx.x; i < bound; i += blockDim.x) tile_expert[i] = -1;
+  for (int i = carry + threadIdx.x; i < bound; i += blockDim.x) tile_info[i] = make_int4(-1, 0, 0, 0);
 }
 
 // Exercises the bounded wait itself: thread 0 waits (at most `limit_ns`) on an
@@ -764,11 +768,11 @@ int ft_tc_tiles_bound(int rows_bound, int G, int ntok) {
   return (rows_bound + ntok - 1) / ntok + (G < rows_bound ? G : rows_bound);
 }
 
-int ft_moe_tile_map(const int* group_offsets, const int* active, int* tile_expert, int* tile_row0,
+int ft_moe_tile_map(const int* group_offsets, const int* active, void* tile_info,
                     int rows_bound, int G, int ntok, cudaStream_t stream) {
-  if (ntok < 1 || G <= 0) return FT_ERR_SHAPE;
+  if (ntok < 1 || G <= 0 || ((uintptr_t)tile_info & 15)) return FT_ERR_SHAPE;
   const int bound = ft_tc_tiles_bound(rows_bound, G, ntok);
-  moe_tile_map_kernel<<<1, 256, 0, stream>>>(group_offsets, active, tile_expert, tile_row0, G, ntok, bound);
+  moe_tile_map_kernel<<<1, 256, 0, stream>>>(group_offsets, active, (int4*)tile_info, G, ntok, bound);
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -779,8 +783,7 @@ int ft_moe_tile_map(const int* group_offsets, const int* active, int* tile_exper
 // `glu`: 0 none; 1 gate and up as two accumulators, weights as the M operand; 2 tokens as
 // the M operand and gate + up rows as one N operand of 256.
 int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc,
-                   const int* group_offsets, const int* active, const int* tile_expert,
-                   const int* tile_row0, const int* c_rows,
+                   const int* group_offsets, const int* active, const void* tile_info, const int* c_rows,
                    const float* row_scale, int* status, int rows_bound, int n_out, int K, int G,
                    int ntok, int glu, int act, float act_alpha, float act_limit,
                    cudaStream_t stream) {
@@ -791,7 +794,7 @@ int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc
   memcpy(&mw, map_w, sizeof(mw));
   memcpy(mx, maps_x, sizeof(mx));
   const int tiles_y = ft_tc_tiles_bound(rows_bound, G, ntok);
-  TcArgs a{C, group_offsets, active, tile_expert, tile_row0, c_rows, row_scale, status, ldc, n_out, K, G, ntok,
+  TcArgs a{C, group_offsets, active, (const int4*)tile_info, c_rows, row_scale, status, ldc, n_out, K, G, ntok,
            tiles_y, act, act_alpha, act_limit};
   static int sms = 0;
   if (!sms) {
@@ -816,8 +819,8 @@ int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc
 // token rows with boxes of 32, 64, 96 and 128 rows (a CTA loads half of a tile's rows);
 // `ntok` (a multiple of 32, at most 256) and the tile map as for ft_moe_gemm_tc.
 int ft_moe_gemm_tc_pair(const void* map_w, const void* maps_x, void* C, long long ldc,
-                        const int* group_offsets, const int* active, const int* tile_expert,
-                        const int* tile_row0, const int* c_rows, const float* row_scale, int* status,
+                        const int* group_offsets, const int* active, const void* tile_info,
+                        const int* c_rows, const float* row_scale, int* status,
                         int rows_bound, int n_out, int K, int G, int ntok, cudaStream_t stream) {
   if (rows_bound <= 0 || n_out <= 0) return FT_OK;
   if (ntok < 32 || ntok > 2 * TC_MAXN || (ntok & 31) || (K & 7) || G <= 0) return FT_ERR_SHAPE;
@@ -825,7 +828,7 @@ int ft_moe_gemm_tc_pair(const void* map_w, const void* maps_x, void* C, long lon
   memcpy(&mw, map_w, sizeof(mw));
   memcpy(mx, maps_x, sizeof(mx));
   const int tiles_y = ft_tc_tiles_bound(rows_bound, G, ntok);
-  TcArgs a{C, group_offsets, active, tile_expert, tile_row0, c_rows, row_scale, status, ldc, n_out, K, G, ntok,
+  TcArgs a{C, group_offsets, active, (const int4*)tile_info, c_rows, row_scale, status, ldc, n_out, K, G, ntok,
            tiles_y, 0, 0.f, 0.f};
   static int sms = 0;
   if (!sms) {

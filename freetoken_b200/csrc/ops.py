@@ -407,21 +407,20 @@ def tc_tokens_per_tile(rows: int, groups: int, wide: bool = False) -> int:
 
 
 def moe_tile_map(group_offsets: torch.Tensor, active: torch.Tensor, rows: int, groups: int,
-                 tokens_per_tile: int, workspace, tag: str = "") -> tuple:
-    """``(tile_expert, tile_row0)`` for the tcgen05 grouped GEMM: one entry per
-    (busy expert, tile of ``tokens_per_tile`` sorted rows).  ``tag`` names the
-    buffers when a step keeps two maps (two tile sizes)."""
+                 tokens_per_tile: int, workspace, tag: str = "") -> torch.Tensor:
+    """The tile list of the tcgen05 grouped GEMM: one int32 quadruple per (busy expert,
+    tile of ``tokens_per_tile`` sorted rows): expert, first row, rows the MMA covers, end of
+    the expert's rows.  ``tag`` names the buffer when a step keeps two lists (two tile sizes)."""
     bound = -(-rows // tokens_per_tile) + min(groups, rows)
-    tile_expert = workspace.get("moe.tile_expert" + tag, (bound,), torch.int32)
-    tile_row0 = workspace.get("moe.tile_row0" + tag, (bound,), torch.int32)
-    f = _fn("moe_gemm_tc", "ft_moe_tile_map", "p p p p i i i")
-    _check(f(_ptr(group_offsets), _ptr(active), _ptr(tile_expert), _ptr(tile_row0), rows, groups,
-             tokens_per_tile, _stream()), "moe_tile_map")
-    return tile_expert, tile_row0
+    tile_info = workspace.get("moe.tile_info" + tag, (bound, 4), torch.int32)
+    f = _fn("moe_gemm_tc", "ft_moe_tile_map", "p p p i i i")
+    _check(f(_ptr(group_offsets), _ptr(active), _ptr(tile_info), rows, groups, tokens_per_tile, _stream()),
+           "moe_tile_map")
+    return tile_info
 
 
 def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offsets: torch.Tensor,
-                active: torch.Tensor, tile_map: tuple, c_rows: Optional[torch.Tensor] = None,
+                active: torch.Tensor, tile_map: torch.Tensor, c_rows: Optional[torch.Tensor] = None,
                 row_scale: Optional[torch.Tensor] = None, rows: int, glu: int = 0,
                 act: str = "silu", act_alpha: float = 1.702, act_limit: float = 7.0,
                 tokens_per_tile: Optional[int] = None) -> None:
@@ -448,16 +447,15 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
         joined = b"".join(bytes(_tc_map(x, x.shape[0], K, x.stride(0), 0, box)) for box in (64, 128, 192, 256))
         maps_x = _TC_MAPS[key] = ctypes.create_string_buffer(joined, 512)
     status = tc_status(x.device)
-    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p p p i i i i i i i f f")
+    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p p i i i i i i i f f")
     _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(maps_x, ctypes.c_void_p), _ptr(c),
-             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map[0]), _ptr(tile_map[1]),
-             _ptr(c_rows), _ptr(row_scale),
+             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map), _ptr(c_rows), _ptr(row_scale),
              _ptr(status), rows, N, K, G, ntok, int(glu), 0 if act == "silu" else 1,
              float(act_alpha), float(act_limit), _stream()), "moe_gemm_tc")
 
 
 def moe_gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offsets: torch.Tensor,
-                     active: torch.Tensor, tile_map: tuple, c_rows: Optional[torch.Tensor] = None,
+                     active: torch.Tensor, tile_map: torch.Tensor, c_rows: Optional[torch.Tensor] = None,
                      row_scale: Optional[torch.Tensor] = None, rows: int, tokens_per_tile: int = 256) -> None:
     """The grouped GEMM without GLU on CTA pairs (``cta_group::2``): two CTAs of a cluster
     share a tile of 256 weight rows by up to 256 tokens, each loading half of both
@@ -476,10 +474,10 @@ def moe_gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group
         joined = b"".join(bytes(_tc_map(x, x.shape[0], K, x.stride(0), 0, box)) for box in (32, 64, 96, 128))
         maps_x = _TC_MAPS[key] = ctypes.create_string_buffer(joined, 512)
     status = tc_status(x.device)
-    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc_pair", "p p p q p p p p p p p i i i i i")
+    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc_pair", "p p p q p p p p p p i i i i i")
     _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(maps_x, ctypes.c_void_p), _ptr(c),
-             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map[0]), _ptr(tile_map[1]),
-             _ptr(c_rows), _ptr(row_scale), _ptr(status), rows, N, K, G, tokens_per_tile, _stream()),
+             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map), _ptr(c_rows), _ptr(row_scale),
+             _ptr(status), rows, N, K, G, tokens_per_tile, _stream()),
            "moe_gemm_tc_pair")
 
 
