@@ -97,12 +97,21 @@ __host__ __device__ __forceinline__ int tc_tile_rows(int r, int ntok) {
 //             Running an expert's short last tile weight-major (N as narrow as its rows) in
 //             the same kernel was measured and is slower, not faster: a tile costs its
 //             bytes, not its products.
+//   TC_TOK    no GLU, token-major like TC_GLUT: up to 128 tokens are the M operand, 256
+//             weight rows (two boxes of 128) the N operand, 256 output features per tile.
+//             A thread of the epilogue owns a token and writes 16 consecutive features
+//             with two 16-byte stores; with the weights as the M operand (TC_PLAIN,
+//             TC_WIDE) it owns a feature and writes one 2-byte value per token, and at 256
+//             rows per expert those stores, not the products, set the pace (measured: the
+//             epilogue warps busy 90 % of the kernel's time, the MMA warp waiting for a
+//             free accumulator 28 % of it; without the stores the kernel ran 1.67 times
+//             as fast).
 // (A variant with gate and up rows side by side in ONE accumulator of up to 256 tokens -
 // an MMA of N = 256 reads less of A per flop from shared memory than two of N = 128 -
 // was built and measured: 642 instead of 392 us at 256 rows per expert; its epilogue,
 // which pairs TMEM lane f with lane f + 64 through shared memory, does not hide under
 // the main loop.)
-enum { TC_GLU2 = 0, TC_PLAIN = 1, TC_WIDE = 2, TC_GLUT = 3 };
+enum { TC_GLU2 = 0, TC_PLAIN = 1, TC_WIDE = 2, TC_GLUT = 3, TC_TOK = 4 };
 
 // Persistent: one CTA per SM walks the tiles t = blockIdx.x, + gridDim.x, ...
 // of the (token tile, weight tile) space, weight tile fastest, so CTAs that run
@@ -118,16 +127,18 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
                                                           const __grid_constant__ CUtensorMap tm_x3,
                                                           TcArgs a) {
   constexpr bool GLU2 = MODE == TC_GLU2, GLUT = MODE == TC_GLUT, GLU = GLU2 || GLUT;
+  constexpr bool TOK = MODE == TC_TOK;                // token-major without GLU
+  constexpr bool TMAJ = GLUT || TOK;                  // tokens are the M operand
   constexpr bool WIDE = MODE == TC_WIDE;
   // a stage holds KSUB 64-wide k-blocks: one with two weight boxes per k-block or wide
   // token boxes, two otherwise, so that every stage moves 40-48 KB and the per-stage
   // barrier round trip is paid half as often on the narrow down projection
   constexpr int TC_B_BYTES = (WIDE ? 2 : 1) * TC_MAXN * TC_BK * 2;   // reserved per k-block
   constexpr int KSUB = MODE == TC_PLAIN ? 2 : 1;
-  constexpr int NA = GLU ? 2 : 1;                     // 16 KB weight regions per k-block
+  constexpr int NA = (GLU || TOK) ? 2 : 1;                   // 16 KB weight regions per k-block
   constexpr int STAGES = MODE == TC_PLAIN ? 3 : 4;
   constexpr int STAGE_BYTES = KSUB * (NA * TC_A_BYTES + TC_B_BYTES);
-  constexpr int FEAT = TC_BM;                         // output features per tile
+  constexpr int FEAT = TOK ? 2 * TC_BM : TC_BM;       // output features per tile
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
@@ -137,7 +148,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ntok = a.ntok;
-  const int acc_cols = GLUT ? 2 * TC_BM : (GLU2 ? 2 * ntok : ntok);   // columns of one accumulator buffer
+  const int acc_cols = TMAJ ? 2 * TC_BM : (GLU2 ? 2 * ntok : ntok);   // columns of one accumulator buffer
   const unsigned tmem_cols = 2 * acc_cols <= 32 ? 32u : (2 * acc_cols <= 64 ? 64u :
                              (2 * acc_cols <= 128 ? 128u : (2 * acc_cols <= 256 ? 256u : 512u)));
   if (threadIdx.x == 0) {
@@ -193,6 +204,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
             const int k = (kb * KSUB + sub) * TC_BK;
             tma_load_3d(st, &tm_w, k, n0, e, &full_bar[s]);
             if (GLU) tma_load_3d(st + TC_A_BYTES, &tm_w, k, a.n_out + n0, e, &full_bar[s]);
+            if (TOK) tma_load_3d(st + TC_A_BYTES, &tm_w, k, n0 + TC_BM, e, &full_bar[s]);
             tma_load_2d(st + NA * TC_A_BYTES, tm_x, k, row0, &full_bar[s]);
           }
         }
@@ -220,7 +232,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
         const int n_tile = cur.z;
         // (token-major GLU: M = 128 token rows, N = 256 weight rows, whatever the tile holds)
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) |
-                               ((unsigned)((GLUT ? 2 * TC_BM : n_tile) >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+                               ((unsigned)((TMAJ ? 2 * TC_BM : n_tile) >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
         const int b = local & 1;
         if (!mbar_wait(&acc_empty[b], ((unsigned)(local >> 1) & 1u) ^ 1u, &gave_up)) {
           atomicCAS(a.status, 0, FT_ST_MOE_MMA_ACC);
@@ -247,7 +259,7 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
             for (int kk = 0; kk < TC_BK / 16; ++kk) {
               const unsigned acc = (kb | sub | kk) != 0;
               const unsigned long long bdesc = sw128_desc(sb + kk * 32);
-              if (GLUT) {                  // A: the token rows; B: gate rows then up rows, 256 in all
+              if (TMAJ) {                  // A: the token rows; B: two boxes of weight rows, 256 in all
                 tc_mma(tmem_d, bdesc, sw128_desc(st + kk * 32), idesc, acc);
                 continue;
               }
@@ -278,10 +290,10 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
       // tile before the wait on the accumulator, so that this tile's main loop hides
       // them; lane l keeps columns l, l+32, ...; handed round by shuffle.  With GLU a
       // column's output row is its sorted row and nothing is loaded.
-      constexpr int NQ = GLU ? 1 : (WIDE ? 2 : 1) * TC_MAXN / 32;
+      constexpr int NQ = (GLU || TOK) ? 1 : (WIDE ? 2 : 1) * TC_MAXN / 32;
       int my_crow[NQ];
       float my_scale[NQ];
-      if (!GLU) {
+      if (!GLU && !TOK) {
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
           const int row = row0 + q * 32 + lane;
@@ -299,26 +311,33 @@ __global__ void __launch_bounds__(192) moe_gemm_tc_kernel(const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const unsigned tmem_d = tmem_base + (unsigned)(b * acc_cols) + ((unsigned)lane_base << 16);
-      if (GLUT) {
-        // TMEM lane = token row of the tile; columns c and c + 128 = gate and up of feature n0 + c
-        const int n0 = (t % wtiles) * TC_BM;
+      if (TMAJ) {
+        // TMEM lane = token row of the tile.  GLU: columns c and c + 128 are gate and up of
+        // feature n0 + c; otherwise column c is feature n0 + c, 256 of them
+        const int n0 = (t % wtiles) * FEAT;
         const int row = row0 + lane_base + lane;
         const bool valid = lane_base + lane < n_tile && row < row_end;
         const int crow = valid ? (a.c_rows ? a.c_rows[row] : row) : 0;
         const float scale = valid && a.row_scale ? a.row_scale[crow] : 1.f;
         __nv_bfloat16* dst = C + (size_t)crow * a.ldc + n0;
         const bool vec = (a.ldc & 7) == 0 && ((uintptr_t)C & 15) == 0;
-        for (int c0 = 0; c0 < TC_BM && n0 + c0 < a.n_out; c0 += 16) {
+        for (int c0 = 0; c0 < FEAT && n0 + c0 < a.n_out; c0 += 16) {
           unsigned g[16], u[16];
           tc_ld16(tmem_d + (unsigned)c0, g);
-          tc_ld16(tmem_d + (unsigned)(TC_BM + c0), u);
+          if (GLUT) tc_ld16(tmem_d + (unsigned)(TC_BM + c0), u);
           tc_ld_wait();
           if (!valid) continue;
           unsigned packed[8];
 #pragma unroll
           for (int c = 0; c < 16; c += 2) {
-            const float v0 = scale * tc_glu(__uint_as_float(g[c]), __uint_as_float(u[c]), a.act, a.act_alpha, a.act_limit);
-            const float v1 = scale * tc_glu(__uint_as_float(g[c + 1]), __uint_as_float(u[c + 1]), a.act, a.act_alpha, a.act_limit);
+            float v0, v1;
+            if (GLUT) {
+              v0 = scale * tc_glu(__uint_as_float(g[c]), __uint_as_float(u[c]), a.act, a.act_alpha, a.act_limit);
+              v1 = scale * tc_glu(__uint_as_float(g[c + 1]), __uint_as_float(u[c + 1]), a.act, a.act_alpha, a.act_limit);
+            } else {
+              v0 = __uint_as_float(g[c]) * scale;
+              v1 = __uint_as_float(g[c + 1]) * scale;
+            }
             const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
             packed[c >> 1] = *reinterpret_cast<const unsigned*>(&h);
           }
@@ -781,14 +800,16 @@ int ft_moe_tile_map(const int* group_offsets, const int* active, void* tile_info
 // maps of the sorted token rows, 128 bytes each, with boxes of 64, 128, 192 and 256 rows.
 // `ntok`: most rows of a token tile (a multiple of 16; up to 128 with GLU, else up to 256).
 // `glu`: 0 none; 1 gate and up as two accumulators, weights as the M operand; 2 tokens as
-// the M operand and gate + up rows as one N operand of 256.
+// the M operand and gate + up rows as one N operand of 256; 3 no GLU, tokens as the M
+// operand and 256 weight rows as the N operand (`ntok` at most 128 for 1 to 3).
 int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc,
                    const int* group_offsets, const int* active, const void* tile_info, const int* c_rows,
                    const float* row_scale, int* status, int rows_bound, int n_out, int K, int G,
                    int ntok, int glu, int act, float act_alpha, float act_limit,
                    cudaStream_t stream) {
   if (rows_bound <= 0 || n_out <= 0) return FT_OK;
-  if (ntok < 16 || ntok > (glu ? TC_MAXN : 2 * TC_MAXN) || (ntok & 15) || (K & 7) || G <= 0 || glu < 0 || glu > 2)
+  if (ntok < 16 || ntok > ((glu == 1 || glu == 2 || glu == 3) ? TC_MAXN : 2 * TC_MAXN) || (ntok & 15) || (K & 7) ||
+      G <= 0 || glu < 0 || glu > 3)
     return FT_ERR_SHAPE;
   CUtensorMap mw, mx[4];
   memcpy(&mw, map_w, sizeof(mw));
@@ -802,11 +823,13 @@ int ft_moe_gemm_tc(const void* map_w, const void* maps_x, void* C, long long ldc
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const int total = tiles_y * ((n_out + TC_BM - 1) / TC_BM);
+  const int feat = glu == 3 ? 2 * TC_BM : TC_BM;
+  const int total = tiles_y * ((n_out + feat - 1) / feat);
   dim3 grid(total < sms ? total : sms);
   constexpr int B_BYTES = TC_MAXN * TC_BK * 2;
   int rc;
-  if (glu == 2) rc = launch_tc<TC_GLUT>(mw, mx, a, grid, 4 * (2 * TC_A_BYTES + B_BYTES) + 1024, stream);
+  if (glu == 3) rc = launch_tc<TC_TOK>(mw, mx, a, grid, 4 * (2 * TC_A_BYTES + B_BYTES) + 1024, stream);
+  else if (glu == 2) rc = launch_tc<TC_GLUT>(mw, mx, a, grid, 4 * (2 * TC_A_BYTES + B_BYTES) + 1024, stream);
   else if (glu) rc = launch_tc<TC_GLU2>(mw, mx, a, grid, 4 * (2 * TC_A_BYTES + B_BYTES) + 1024, stream);
   else if (ntok > TC_MAXN) rc = launch_tc<TC_WIDE>(mw, mx, a, grid, 4 * (TC_A_BYTES + 2 * B_BYTES) + 1024, stream);
   else rc = launch_tc<TC_PLAIN>(mw, mx, a, grid, 3 * 2 * (TC_A_BYTES + B_BYTES) + 1024, stream);

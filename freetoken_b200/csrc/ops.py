@@ -421,15 +421,18 @@ def moe_tile_map(group_offsets: torch.Tensor, active: torch.Tensor, rows: int, g
 
 def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offsets: torch.Tensor,
                 active: torch.Tensor, tile_map: torch.Tensor, c_rows: Optional[torch.Tensor] = None,
-                row_scale: Optional[torch.Tensor] = None, rows: int, glu: int = 0,
-                act: str = "silu", act_alpha: float = 1.702, act_limit: float = 7.0,
+                row_scale: Optional[torch.Tensor] = None, rows: int, glu: bool = False,
+                token_major: bool = False, act: str = "silu", act_alpha: float = 1.702, act_limit: float = 7.0,
                 tokens_per_tile: Optional[int] = None) -> None:
     """Grouped expert GEMM on tcgen05/TMEM fed by TMA.  ``x`` holds the sorted
     rows ``[>= rows, K]`` (already gathered), ``w`` is ``[G, N_w, K]``; same
     output conventions as :func:`gemm_rows`.  ``tile_map`` comes from
     :func:`moe_tile_map` with the same ``tokens_per_tile`` (at most 128 with GLU, else 256).
-    ``glu``: 0 none; 1 (or True) gate and up as two accumulators with the weights as the
-    M operand; 2 token-major (tokens the M operand, gate + up rows one N operand of 256)."""
+    ``token_major``: up to 128 tokens are the MMA's M operand and 256 weight rows its N
+    operand (with ``glu``: 128 gate rows and the 128 up rows of the same features), a thread
+    of the epilogue owns a token and stores 16 features at a time; otherwise the weights are
+    the M operand (with ``glu``: gate and up as two accumulators) and the tile is as narrow
+    as the tokens it holds."""
     if not moe_gemm_tc_takes(x, w, c):
         raise KernelError("moe_gemm_tc: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
     G, NW, K = w.shape
@@ -439,6 +442,7 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
     for name, t in (("group_offsets", group_offsets), ("active", active)):
         _need(t, name, torch.int32)
     ntok = tokens_per_tile or tc_tokens_per_tile(rows, G)
+    form = (2 if token_major else 1) if glu else (3 if token_major else 0)
     map_w = _tc_map(w, NW, K, K, G, 128)
     # the token rows through boxes of 64, 128, 192 and 256 rows: a tile takes the smallest that holds it
     key = ("x4", x.data_ptr(), x.shape[0], K, x.stride(0))
@@ -450,7 +454,7 @@ def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offs
     f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p p i i i i i i i f f")
     _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(maps_x, ctypes.c_void_p), _ptr(c),
              c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map), _ptr(c_rows), _ptr(row_scale),
-             _ptr(status), rows, N, K, G, ntok, int(glu), 0 if act == "silu" else 1,
+             _ptr(status), rows, N, K, G, ntok, form, 0 if act == "silu" else 1,
              float(act_alpha), float(act_limit), _stream()), "moe_gemm_tc")
 
 
@@ -497,14 +501,12 @@ def moe_experts_tc(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tenso
     token_major = -(-rows // max(1, G)) >= TC_GLU_TOKEN_MAJOR_FROM_ROWS
     tiles = moe_tile_map(group_offsets, active, rows, G, ntok, workspace)
     moe_gemm_tc(xs, w_gate_up, mid, group_offsets=group_offsets, active=active, tile_map=tiles,
-                rows=rows, glu=2 if token_major else 1, act=act, act_alpha=act_alpha, act_limit=act_limit,
+                rows=rows, glu=True, token_major=token_major, act=act, act_alpha=act_alpha, act_limit=act_limit,
                 tokens_per_tile=ntok)
-    # the down projection takes wider token tiles when experts are busy enough
-    ntok2 = tc_tokens_per_tile(rows, G, wide=True)
-    if ntok2 != ntok:
-        tiles = moe_tile_map(group_offsets, active, rows, G, ntok2, workspace, tag=".wide")
+    # the down projection runs token-major at every load (level with the weight-major forms up
+    # to 192 rows per expert, 10 to 30 % faster beyond) and shares the tile list
     moe_gemm_tc(mid, w_down, parts, group_offsets=group_offsets, active=active, tile_map=tiles,
-                c_rows=sorted_route, row_scale=route_weight, rows=rows, tokens_per_tile=ntok2)
+                c_rows=sorted_route, row_scale=route_weight, rows=rows, token_major=True, tokens_per_tile=ntok)
 
 
 def pass_rows(rows: int) -> int:
