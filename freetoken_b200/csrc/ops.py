@@ -382,107 +382,64 @@ def moe_gemm_tc_takes(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> bool
             and c.stride(1) == 1)
 
 
-# From this many sorted rows per expert (on average) the down projection of the grouped
-# GEMM takes token tiles of up to 256 rows (measured with 64 experts of real width: at 64
-# rows per expert 122 against 115 us, at 128 rows 134 against 138, at 512 rows 379 against
-# 402).  gate_up + GLU keeps two accumulators of up to 128 tokens: all of TMEM otherwise.
-TC_WIDE_FROM_ROWS = int(os.environ.get("FREETOKEN_TC_WIDE_FROM_ROWS", "96"))
 # From this many sorted rows per expert (on average) gate_up + GLU runs token-major: the
-# tokens are the MMA's M operand, gate and up rows one N operand of 256.
-# (measured with 256 experts of real width: level at 128 and 192 rows per expert, 10 %
-# faster at 256, 2 % at 512; 12 % with 64 experts of 512 rows).
-TC_GLU_TOKEN_MAJOR_FROM_ROWS = int(os.environ.get("FREETOKEN_TC_GLU_TOKEN_MAJOR_FROM_ROWS", "224"))
-
-
-def tc_tokens_per_tile(rows: int, groups: int, wide: bool = False) -> int:
-    """Most tokens of an MMA tile for ``rows`` sorted rows over ``groups`` experts.
-    A tile's product is as wide as the rows it really holds (rounded up to 16) and an
-    expert's rows are dealt out evenly over its tiles, so a large limit costs nothing
-    extra: 256 when experts are busy (``wide`` says the caller's kernel takes that),
-    else 128."""
-    avg = -(-rows // max(1, groups))
-    if wide and avg >= TC_WIDE_FROM_ROWS:
-        return 256
-    return 128
+# tokens are the MMA's M operand, gate and up rows one N operand of 256 (measured with 256
+# experts of real width against the weight-major form: 767 against 758 us at 64 rows per
+# expert, level at 96, 905 against 919 at 128, 1,115 against 1,191 at 192, 1,343 against
+# 1,480 at 256).  The down projection is token-major at every load.
+TC_GLU_TOKEN_MAJOR_FROM_ROWS = int(os.environ.get("FREETOKEN_TC_GLU_TOKEN_MAJOR_FROM_ROWS", "112"))
+TC_TOKENS_PER_TILE = 128
 
 
 def moe_tile_map(group_offsets: torch.Tensor, active: torch.Tensor, rows: int, groups: int,
-                 tokens_per_tile: int, workspace, tag: str = "") -> torch.Tensor:
+                 workspace) -> torch.Tensor:
     """The tile list of the tcgen05 grouped GEMM: one int32 quadruple per (busy expert,
-    tile of ``tokens_per_tile`` sorted rows): expert, first row, rows the MMA covers, end of
-    the expert's rows.  ``tag`` names the buffer when a step keeps two lists (two tile sizes)."""
-    bound = -(-rows // tokens_per_tile) + min(groups, rows)
-    tile_info = workspace.get("moe.tile_info" + tag, (bound, 4), torch.int32)
+    tile of up to 128 sorted rows): expert, first row, rows the MMA covers, end of the
+    expert's rows.  An expert's rows are dealt out evenly over its tiles."""
+    for name, t in (("group_offsets", group_offsets), ("active", active)):
+        _need(t, name, torch.int32)
+    bound = -(-rows // TC_TOKENS_PER_TILE) + min(groups, rows)
+    tile_info = workspace.get("moe.tile_info", (bound, 4), torch.int32)
     f = _fn("moe_gemm_tc", "ft_moe_tile_map", "p p p i i i")
-    _check(f(_ptr(group_offsets), _ptr(active), _ptr(tile_info), rows, groups, tokens_per_tile, _stream()),
+    _check(f(_ptr(group_offsets), _ptr(active), _ptr(tile_info), rows, groups, TC_TOKENS_PER_TILE, _stream()),
            "moe_tile_map")
     return tile_info
 
 
-def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offsets: torch.Tensor,
-                active: torch.Tensor, tile_map: torch.Tensor, c_rows: Optional[torch.Tensor] = None,
-                row_scale: Optional[torch.Tensor] = None, rows: int, glu: bool = False,
-                token_major: bool = False, act: str = "silu", act_alpha: float = 1.702, act_limit: float = 7.0,
-                tokens_per_tile: Optional[int] = None) -> None:
+def moe_gemm_tc(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, tile_map: torch.Tensor,
+                c_rows: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
+                rows: int, glu: bool = False, token_major: bool = True, act: str = "silu",
+                act_alpha: float = 1.702, act_limit: float = 7.0) -> None:
     """Grouped expert GEMM on tcgen05/TMEM fed by TMA.  ``x`` holds the sorted
     rows ``[>= rows, K]`` (already gathered), ``w`` is ``[G, N_w, K]``; same
-    output conventions as :func:`gemm_rows`.  ``tile_map`` comes from
-    :func:`moe_tile_map` with the same ``tokens_per_tile`` (at most 128 with GLU, else 256).
+    output conventions as :func:`gemm_rows`.  ``tile_map`` comes from :func:`moe_tile_map`.
     ``token_major``: up to 128 tokens are the MMA's M operand and 256 weight rows its N
     operand (with ``glu``: 128 gate rows and the 128 up rows of the same features), a thread
-    of the epilogue owns a token and stores 16 features at a time; otherwise the weights are
-    the M operand (with ``glu``: gate and up as two accumulators) and the tile is as narrow
+    of the epilogue owns a token and stores 16 features at a time; otherwise (``glu`` only)
+    the weights are the M operand, gate and up two accumulators, and a tile is as narrow
     as the tokens it holds."""
     if not moe_gemm_tc_takes(x, w, c):
         raise KernelError("moe_gemm_tc: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
+    if not glu and not token_major:
+        raise KernelError("moe_gemm_tc: the weight-major form exists with GLU only")
     G, NW, K = w.shape
     N = NW // 2 if glu else NW
     if x.shape[1] != K or c.shape[1] != N:
         raise KernelError("moe_gemm_tc: shapes do not match")
-    for name, t in (("group_offsets", group_offsets), ("active", active)):
-        _need(t, name, torch.int32)
-    ntok = tokens_per_tile or tc_tokens_per_tile(rows, G)
-    form = (2 if token_major else 1) if glu else (3 if token_major else 0)
+    form = (1 if token_major else 0) if glu else 2
     map_w = _tc_map(w, NW, K, K, G, 128)
-    # the token rows through boxes of 64, 128, 192 and 256 rows: a tile takes the smallest that holds it
-    key = ("x4", x.data_ptr(), x.shape[0], K, x.stride(0))
+    # the token rows through boxes of 64 and 128 rows: a tile takes the smaller if it holds it
+    key = ("x2", x.data_ptr(), x.shape[0], K, x.stride(0))
     maps_x = _TC_MAPS.get(key)
     if maps_x is None:
-        joined = b"".join(bytes(_tc_map(x, x.shape[0], K, x.stride(0), 0, box)) for box in (64, 128, 192, 256))
-        maps_x = _TC_MAPS[key] = ctypes.create_string_buffer(joined, 512)
+        joined = b"".join(bytes(_tc_map(x, x.shape[0], K, x.stride(0), 0, box)) for box in (64, 128))
+        maps_x = _TC_MAPS[key] = ctypes.create_string_buffer(joined, 256)
     status = tc_status(x.device)
-    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p p p i i i i i i i f f")
+    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc", "p p p q p p p p i i i i i i i f f")
     _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(maps_x, ctypes.c_void_p), _ptr(c),
-             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map), _ptr(c_rows), _ptr(row_scale),
-             _ptr(status), rows, N, K, G, ntok, form, 0 if act == "silu" else 1,
-             float(act_alpha), float(act_limit), _stream()), "moe_gemm_tc")
-
-
-def moe_gemm_tc_pair(x: torch.Tensor, w: torch.Tensor, c: torch.Tensor, *, group_offsets: torch.Tensor,
-                     active: torch.Tensor, tile_map: torch.Tensor, c_rows: Optional[torch.Tensor] = None,
-                     row_scale: Optional[torch.Tensor] = None, rows: int, tokens_per_tile: int = 256) -> None:
-    """The grouped GEMM without GLU on CTA pairs (``cta_group::2``): two CTAs of a cluster
-    share a tile of 256 weight rows by up to 256 tokens, each loading half of both
-    operands.  Same conventions as :func:`moe_gemm_tc`; ``tokens_per_tile`` a multiple of 32."""
-    if not moe_gemm_tc_takes(x, w, c):
-        raise KernelError("moe_gemm_tc_pair: needs bfloat16 operands, K % 8 == 0 and 16-byte aligned rows")
-    G, N, K = w.shape
-    if x.shape[1] != K or c.shape[1] != N:
-        raise KernelError("moe_gemm_tc_pair: shapes do not match")
-    for name, t in (("group_offsets", group_offsets), ("active", active)):
-        _need(t, name, torch.int32)
-    map_w = _tc_map(w, N, K, K, G, 128)
-    key = ("x4pair", x.data_ptr(), x.shape[0], K, x.stride(0))
-    maps_x = _TC_MAPS.get(key)
-    if maps_x is None:
-        joined = b"".join(bytes(_tc_map(x, x.shape[0], K, x.stride(0), 0, box)) for box in (32, 64, 96, 128))
-        maps_x = _TC_MAPS[key] = ctypes.create_string_buffer(joined, 512)
-    status = tc_status(x.device)
-    f = _fn("moe_gemm_tc", "ft_moe_gemm_tc_pair", "p p p q p p p p p p i i i i i")
-    _check(f(ctypes.cast(map_w, ctypes.c_void_p), ctypes.cast(maps_x, ctypes.c_void_p), _ptr(c),
-             c.stride(0), _ptr(group_offsets), _ptr(active), _ptr(tile_map), _ptr(c_rows), _ptr(row_scale),
-             _ptr(status), rows, N, K, G, tokens_per_tile, _stream()),
-           "moe_gemm_tc_pair")
+             c.stride(0), _ptr(tile_map), _ptr(c_rows), _ptr(row_scale), _ptr(status), rows, N, K, G,
+             TC_TOKENS_PER_TILE, form, 0 if act == "silu" else 1, float(act_alpha), float(act_limit),
+             _stream()), "moe_gemm_tc")
 
 
 def moe_experts_tc(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, mid: torch.Tensor,
@@ -497,16 +454,11 @@ def moe_experts_tc(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tenso
     G = w_gate_up.shape[0]
     xs = workspace.get("moe.sorted_x", (rows, x.shape[1]), x.dtype)
     gather_rows(x, sorted_token, xs)
-    ntok = tc_tokens_per_tile(rows, G)
-    token_major = -(-rows // max(1, G)) >= TC_GLU_TOKEN_MAJOR_FROM_ROWS
-    tiles = moe_tile_map(group_offsets, active, rows, G, ntok, workspace)
-    moe_gemm_tc(xs, w_gate_up, mid, group_offsets=group_offsets, active=active, tile_map=tiles,
-                rows=rows, glu=True, token_major=token_major, act=act, act_alpha=act_alpha, act_limit=act_limit,
-                tokens_per_tile=ntok)
-    # the down projection runs token-major at every load (level with the weight-major forms up
-    # to 192 rows per expert, 10 to 30 % faster beyond) and shares the tile list
-    moe_gemm_tc(mid, w_down, parts, group_offsets=group_offsets, active=active, tile_map=tiles,
-                c_rows=sorted_route, row_scale=route_weight, rows=rows, token_major=True, tokens_per_tile=ntok)
+    tiles = moe_tile_map(group_offsets, active, rows, G, workspace)
+    busy_experts = -(-rows // max(1, G)) >= TC_GLU_TOKEN_MAJOR_FROM_ROWS
+    moe_gemm_tc(xs, w_gate_up, mid, tile_map=tiles, rows=rows, glu=True, token_major=busy_experts, act=act,
+                act_alpha=act_alpha, act_limit=act_limit)
+    moe_gemm_tc(mid, w_down, parts, tile_map=tiles, c_rows=sorted_route, row_scale=route_weight, rows=rows)
 
 
 def pass_rows(rows: int) -> int:

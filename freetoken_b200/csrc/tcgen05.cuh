@@ -146,56 +146,4 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// ---- CTA pairs (`cta_group::2`): two CTAs of a cluster run one MMA of M = 256 ----------
-// Each CTA holds its 128 rows of A and half of the rows of B in its own shared memory, at
-// the same offsets; the even CTA of the pair (the leader) issues the MMA, which reads both
-// CTAs' shared memory and writes 128 accumulator rows into each CTA's TMEM.
-__device__ __forceinline__ unsigned cluster_ctarank() {
-  unsigned r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// The shared::cluster address of `p` (a shared-memory object of this CTA) in CTA `rank`.
-__device__ __forceinline__ unsigned cluster_addr_of(const void* p, unsigned rank) {
-  unsigned a;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(p)), "r"(rank));
-  return a;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// TMA tile loads of a CTA pair: the bytes land in THIS CTA's shared memory and are counted
-// on the barrier at `bar_cluster_addr`, which may be the other CTA's.
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y,
-                                                 unsigned bar_cluster_addr) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, int x, int y, int z,
-                                                 unsigned bar_cluster_addr) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr) : "memory");
-}
-__device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
-                                            unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// Arrives, once the pair's MMAs issued so far are complete, on the barrier at this offset
-// in BOTH CTAs of the pair (a signal, not a load: no data is multicast).
-__device__ __forceinline__ void tc_commit_pair(unsigned long long* bar) {
-  const unsigned short mask = 3;
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(smem_u32(bar)), "h"(mask) : "memory");
-}
-
 }  // namespace ft

@@ -9,7 +9,7 @@ repetitions so that no repetition finds it in L2.
 
 Kernels: ``expert_gemv`` (decode experts, weight-streaming mma.sync kernel),
 ``lm_head`` (the same kernel, dense, float32 result), ``moe_gemm_tc`` (prefill
-experts on tcgen05/TMEM with TMA), ``attn_decode`` (64 rows x 2,048 keys; ``_32k``: 8 rows x 32,768 keys), ``attn_prefill`` (mma.sync), ``attn_prefill_tc`` (tcgen05/TMEM, TMA-fed; ``_8k``: a
+experts on tcgen05/TMEM with TMA, 64 rows per expert; ``_busy``: 512 rows per expert), ``attn_decode`` (64 rows x 2,048 keys; ``_32k``: 8 rows x 32,768 keys), ``attn_prefill`` (mma.sync), ``attn_prefill_tc`` (tcgen05/TMEM, TMA-fed; ``_8k``: a
 8,192-token prompt),
 ``router`` (float32 router logits + top-k for a decode batch); ``*_flashinfer``: the same
 attention shapes through FlashInfer's trtllm-gen kernels (the reference's backend on
@@ -79,31 +79,34 @@ def lm_head(sets: int = 2):
     return (lambda i: ops.skinny_gemm(x, w[i % sets], out)), V * H * 2, 0.0, "hbm"
 
 
-def moe_gemm_tc(sets: int = 1):
-    """Prefill: 512 tokens x 8 routes over 64 experts (64 rows each), 1.8 GB of weights."""
-    E, T, k = 64, 512, 8
+def _moe_gemm_tc(E: int, T: int, sets: int):
+    k = 8
     w1 = [torch.randn(E, 2 * I, H, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
     w2 = [torch.randn(E, H, I, device=DEV, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
     x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
     route, token, offsets, active, busy = _routes(E, T, k)
     R = T * k
     ws = Workspace(DEV)
-    xs = torch.empty(R, H, device=DEV, dtype=torch.bfloat16)
-    ops.gather_rows(x, token, xs)
     mid = torch.empty(R, I, device=DEV, dtype=torch.bfloat16)
     parts = torch.empty(R, H, device=DEV, dtype=torch.bfloat16)
     rw = torch.rand(R, device=DEV)
-    ntok = ops.tc_tokens_per_tile(R, E)
-    tiles = ops.moe_tile_map(offsets, active, R, E, ntok, ws)
-    ntok2 = ops.tc_tokens_per_tile(R, E, wide=True)
-    tiles2 = tiles if ntok2 == ntok else ops.moe_tile_map(offsets, active, R, E, ntok2, ws, tag=".wide")
 
-    def run(i):
-        ops.moe_gemm_tc(xs, w1[i % sets], mid, group_offsets=offsets, active=active, tile_map=tiles, rows=R,
-                        glu=True, tokens_per_tile=ntok)
-        ops.moe_gemm_tc(mid, w2[i % sets], parts, group_offsets=offsets, active=active, tile_map=tiles2,
-                        c_rows=route, row_scale=rw, rows=R, tokens_per_tile=ntok2)
-    return run, busy * 3 * I * H * 2, 2.0 * R * 3 * I * H, "hbm"
+    def run(i):     # gather + tile list + both products, as a step runs them
+        ops.moe_experts_tc(x, w1[i % sets], w2[i % sets], mid, parts, offsets, active, route, token, rw, R,
+                           "silu", 1.702, 7.0, ws)
+    return run, busy * 3 * I * H * 2, 2.0 * R * 3 * I * H
+
+
+def moe_gemm_tc(sets: int = 1):
+    """Prefill: 512 tokens x 8 routes over 64 experts (64 rows each), 1.8 GB of weights."""
+    run, nbytes, flops = _moe_gemm_tc(64, 512, sets)
+    return run, nbytes, flops, "hbm"
+
+
+def moe_gemm_tc_busy(sets: int = 1):
+    """Prefill with busy experts: 4,096 tokens x 8 routes over 64 experts (512 rows each)."""
+    run, nbytes, flops = _moe_gemm_tc(64, 4096, sets)
+    return run, nbytes, flops, "flops"
 
 
 def _kv(batch: int, ctx: int, sets: int):
@@ -251,7 +254,7 @@ def router(sets: int = 8):
 
 
 KERNELS: Dict[str, Callable[[], Tuple[Callable[[int], None], int, float, str]]] = {
-    "expert_gemv": expert_gemv, "lm_head": lm_head, "moe_gemm_tc": moe_gemm_tc,
+    "expert_gemv": expert_gemv, "lm_head": lm_head, "moe_gemm_tc": moe_gemm_tc, "moe_gemm_tc_busy": moe_gemm_tc_busy,
     "attn_decode": attn_decode, "attn_decode_32k": attn_decode_32k, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
     "attn_prefill_8k": attn_prefill_8k, "attn_prefill_tc_8k": attn_prefill_tc_8k, "router": router,
     "peak_copy": peak_copy, "peak_read": peak_read, "peak_gemm": peak_gemm,
