@@ -21,18 +21,36 @@ __device__ __forceinline__ void select_token(const float* __restrict__ x, const 
                                              int E, int k, int softmax_scoring, int renormalize, float scale,
                                              int terms, int lane, int& my_id, float& my_w) {
   // a row holds `terms` partial logits per expert, E apart (the router weight
-  // split into bfloat16 terms); they are summed in order, in float32
-  auto logit = [&](int e) {
-    float v = x[e];
-    for (int p = 1; p < terms; ++p) v += x[p * E + e];
-    return v;
+  // split into bfloat16 terms); they are summed in order, in float32.  A lane takes
+  // experts lane, lane + 32, ...; it fetches eight of them at a time into registers
+  // before it touches shared memory, so that its loads from global memory are in flight
+  // together (one after the other they were most of this function's time: each waits
+  // for L2)
+  constexpr int EPL = 8;
+  auto load_logits = [&](int base, float (&v)[EPL]) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int e = base + i * 32 + lane;
+      v[i] = e < E ? x[e] : 0.f;
+    }
+    for (int p = 1; p < terms; ++p) {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const int e = base + i * 32 + lane;
+        if (e < E) v[i] += x[p * E + e];
+      }
+    }
   };
   if (softmax_scoring) {
     float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) {
-      const float v = logit(e);
-      score[e] = v;
-      mx = fmaxf(mx, v);
+    for (int base = 0; base < E; base += 32 * EPL) {
+      float v[EPL];
+      load_logits(base, v);
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const int e = base + i * 32 + lane;
+        if (e < E) { score[e] = v[i]; mx = fmaxf(mx, v[i]); }
+      }
     }
     mx = warp_max(mx);
     float sum = 0.f;
@@ -44,9 +62,29 @@ __device__ __forceinline__ void select_token(const float* __restrict__ x, const 
     sum = warp_sum(sum);
     for (int e = lane; e < E; e += 32) score[e] = score[e] / sum;
   } else {
-    for (int e = lane; e < E; e += 32) score[e] = 1.f / (1.f + expf(-logit(e)));
+    for (int base = 0; base < E; base += 32 * EPL) {
+      float v[EPL];
+      load_logits(base, v);
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const int e = base + i * 32 + lane;
+        if (e < E) score[e] = 1.f / (1.f + expf(-v[i]));
+      }
+    }
   }
-  for (int e = lane; e < E; e += 32) choice[e] = score[e] + (bias ? bias[e] : 0.f);
+  for (int base = 0; base < E; base += 32 * EPL) {
+    float b[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int e = base + i * 32 + lane;
+      b[i] = (bias && e < E) ? bias[e] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int e = base + i * 32 + lane;
+      if (e < E) choice[e] = score[e] + b[i];
+    }
+  }
   __syncwarp();
   float wsum = 0.f;
   my_id = 0;            // lane j keeps the j-th choice (k <= 32), else it goes through memory
