@@ -13,7 +13,7 @@ with the last row as the sink for padded rows
 
 from __future__ import annotations
 
-from typing import Dict, List, Sequence
+from typing import List, Sequence
 
 import torch
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Dict, Optional, Sequence
+from typing import Dict, Optional
 
 import torch
 

@@ -19,7 +19,7 @@ logits are returned so that sampling stays a separate, testable step.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, Hashable, List, Mapping, Optional, Sequence, Tuple
 
 import numpy as np
@@ -31,7 +31,7 @@ from ..csrc import build, ops
 from ..models.model import Model
 from ..parts import linear
 from ..parts.base import CacheView, Segment, StepContext, StepShape, Workspace
-from ..registry import Architecture, architecture_of, get_architecture, read_model_config
+from ..registry import Architecture, architecture_of, read_model_config
 from ..weights.loader import check_state, load_tensors
 from ..weights.random_init import RandomOptions, random_state
 

@@ -32,7 +32,7 @@ from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, Iterable, List, Optional, Sequence, Tuple
+from typing import Deque, Hashable, Iterable, List, Optional, Sequence
 
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams

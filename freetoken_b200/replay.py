@@ -26,7 +26,6 @@ import os
 import sys
 from typing import List, Optional
 
-import numpy as np
 
 
 def build_parser() -> argparse.ArgumentParser:

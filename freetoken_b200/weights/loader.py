@@ -16,12 +16,12 @@ copy of a stacked expert bank is ever made
 
 from __future__ import annotations
 
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from .safetensors_io import Checkpoint
-from .spec import Cat, Name, Source, Stack, TensorSpec, device_dtype, leaves
+from .spec import Cat, Name, Source, TensorSpec, device_dtype, leaves
 
 
 class WeightError(RuntimeError):

@@ -20,8 +20,8 @@ Roles and the dtype a tensor has on the device:
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import List, Optional, Sequence, Tuple, Union
+from dataclasses import dataclass
+from typing import List, Tuple, Union
 
 import torch
 

@@ -26,7 +26,6 @@ residual stream stay float32.
 from __future__ import annotations
 
 import json
-import math
 import os
 import struct
 from typing import Dict, List, Optional, Tuple

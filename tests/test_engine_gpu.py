@@ -2,7 +2,6 @@
 mixed batches with page reuse; in float32 and bfloat16; two (three) tiny
 configurations that differ in every size and option."""
 
-import os
 
 import pytest
 import torch

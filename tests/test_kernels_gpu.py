@@ -2,7 +2,6 @@
 op, at sizes other than the engine's tiny models (odd widths, head sizes that
 are no power of two, groups of 1/3/6, vocabularies like 1000)."""
 
-import math
 
 import pytest
 import torch

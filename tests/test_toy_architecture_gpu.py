@@ -5,7 +5,6 @@ model folder and stepped - whole, in portions and in mixed batches - without a
 change to any file of the framework, and agrees with a plain implementation
 written beside it."""
 
-import json
 import os
 from dataclasses import dataclass
 from typing import List

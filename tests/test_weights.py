@@ -9,7 +9,7 @@ import torch
 import tiny
 from freetoken_b200.models import Model
 from freetoken_b200.registry import architecture_of
-from freetoken_b200.weights import (Checkpoint, Init, Name, TensorSpec, WeightError, device_dtype,
+from freetoken_b200.weights import (Checkpoint, Name, TensorSpec, WeightError, device_dtype,
                                     load_tensors, plan_loading, write_model_folder, write_safetensors)
 from plain_model import read_safetensors
 

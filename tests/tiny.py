@@ -11,7 +11,6 @@ tensor-core kernels take.
 
 from __future__ import annotations
 
-import os
 from typing import Dict, List
 
 import torch
