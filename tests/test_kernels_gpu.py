@@ -189,7 +189,7 @@ def _grouped_case(E, k, T, seed=0):
                                            (4, 2, 400, 96, 144, "swigluoai"),  # 200 rows per expert
                                            (16, 4, 150, 128, 80, "silu"), (3, 1, 40, 40, 24, "silu"),
                                            (8, 2, 700, 264, 200, "silu"),
-                                           (4, 2, 650, 136, 72, "silu"),      # 325 rows per expert: wide tiles
+                                           (4, 2, 650, 136, 72, "silu"),      # 325 rows per expert: three tiles each
                                            (1, 1, 300, 128, 80, "silu")])     # a single expert: still a 3-D weight map
 def test_expert_gemms(kernel, E, k, T, H, I, act, monkeypatch):
     """gate_up + GLU, then down with the route weight, against a per-route loop."""
@@ -241,6 +241,33 @@ def test_expert_gemms(kernel, E, k, T, H, I, act, monkeypatch):
         assert torch.allclose(got_mid, m, atol=tol["atol"], rtol=tol["rtol"]), (e, "mid")
         y = (got_mid @ w2[e].float().t()) * rw[rs][:, None]
         assert torch.allclose(parts[rs].float(), y, atol=tol["atol"], rtol=tol["rtol"]), (e, "down")
+
+
+def test_moe_tile_map_covers_every_row_once_with_even_tiles():
+    """The tile list of the tcgen05 grouped GEMM: per busy expert the fewest tiles of at
+    most 128 rows, of equal size (in steps of 16), in expert order; empty entries after."""
+    from freetoken_b200.parts.base import Workspace
+    o = ops()
+    counts = [0, 1, 700, 0, 128, 129, 260, 16, 0, 300]
+    E = len(counts)
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    busy = [e for e, c in enumerate(counts) if c]
+    active = torch.tensor(busy + [0] * (E - len(busy)) + [len(busy)], dtype=torch.int32, device=DEV)
+    rows = sum(counts)
+    info = o.moe_tile_map(offsets, active, rows, E, Workspace(DEV)).cpu().tolist()
+    want = []
+    for e in busy:
+        r, begin = counts[e], int(offsets[e])
+        tiles = -(-r // 128)
+        size = 128 if tiles == 1 else min(128, -(-(-(-r // tiles)) // 16) * 16)
+        for i in range(tiles):
+            row0 = begin + i * size
+            left = begin + r - row0
+            want.append([e, row0, min(size, -(-left // 16) * 16), begin + r])
+    assert info[:len(want)] == want
+    assert all(entry[0] == -1 for entry in info[len(want):])
+    covered = sorted(row for e, row0, n, end in want for row in range(row0, min(row0 + n, end)))
+    assert covered == list(range(rows))
 
 
 @pytest.mark.parametrize("ct", ["bfloat16", "float32"])
