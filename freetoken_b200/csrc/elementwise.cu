@@ -248,6 +248,17 @@ __global__ void qk_rope_store_kernel(QkRopeArgs a) {
 // pairing with rotary_dim % 16 == 0, so that a piece of 8 elements below R/2
 // pairs with the piece R/2 further on.
 struct Chunk8 { float v[8]; };
+__device__ __forceinline__ Chunk8 unpack8(const uint4& raw) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  Chunk8 c;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    c.v[2 * i] = f.x;
+    c.v[2 * i + 1] = f.y;
+  }
+  return c;
+}
 __device__ __forceinline__ Chunk8 load8(const __nv_bfloat16* p) {
   const uint4 raw = *reinterpret_cast<const uint4*>(p);
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -320,9 +331,23 @@ __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
   const int qn = a.nq * d, kn = a.nkv * d;
   float inv_q = 1.f, inv_k = 1.f;
   if (a.norm_mode == 1) {
+    // a thread's pieces four at a time: fetched together, summed in the same order as one by one
     float sq = 0.f, sk = 0.f;
-    for (int c = threadIdx.x; c < (qn >> 3); c += blockDim.x) sq += sumsq8(load8(row + c * 8));
-    for (int c = threadIdx.x; c < (kn >> 3); c += blockDim.x) sk += sumsq8(load8(row + qn + c * 8));
+    auto sum_pieces = [&](const __nv_bfloat16* base, int pieces, float& acc) {
+      for (int c0 = threadIdx.x; c0 < pieces; c0 += 4 * blockDim.x) {
+        uint4 raw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * blockDim.x;
+          raw[u] = c < pieces ? *reinterpret_cast<const uint4*>(base + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (c0 + u * (int)blockDim.x < pieces) acc += sumsq8(unpack8(raw[u]));
+      }
+    };
+    sum_pieces(row, qn >> 3, sq);
+    sum_pieces(row + qn, kn >> 3, sk);
     block_sum2(sq, sk, scratch);
     inv_q = rsqrtf(sq / (float)qn + a.eps);
     inv_k = rsqrtf(sk / (float)kn + a.eps);
