@@ -56,7 +56,13 @@ __device__ __forceinline__ void store4f(__nv_bfloat16* p, float4 v) {
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
-template <typename AT, bool VEC>
+// EAGER (a step of few tokens, where a launch is a chain of waits for L2 rather than a
+// stream): the k partial rows of a piece are fetched four at a time before they are added,
+// in the same order.  With every SM full of such blocks the extra loads in flight cost more
+// than they save (25 -> 29 us at 2,048 tokens), so many tokens keep the one-by-one loop.
+constexpr int ROW_KERNEL_EAGER_TOKENS = 64;   // up to this many tokens the row kernels fetch eagerly
+
+template <typename AT, bool VEC, bool EAGER = false>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_kernel(const AT* __restrict__ delta, float* __restrict__ residual,
                const float* __restrict__ weight, AT* __restrict__ out, int H, float eps,
@@ -79,9 +85,21 @@ rmsnorm_kernel(const AT* __restrict__ delta, float* __restrict__ residual,
         float4 z = load4f(r + 4 * gi);
         if (d) {
           float4 add = load4f(d + 4 * gi);
-          for (int q = 1; q < k; ++q) {
-            const float4 more = load4f(d + (size_t)q * H + 4 * gi);
-            add.x += more.x; add.y += more.y; add.z += more.z; add.w += more.w;
+          if (EAGER) {
+            for (int q0 = 1; q0 < k; q0 += 4) {
+              float4 more[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                more[u] = q0 + u < k ? load4f(d + (size_t)(q0 + u) * H + 4 * gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (q0 + u < k) { add.x += more[u].x; add.y += more[u].y; add.z += more[u].z; add.w += more[u].w; }
+            }
+          } else {
+            for (int q = 1; q < k; ++q) {
+              const float4 more = load4f(d + (size_t)q * H + 4 * gi);
+              add.x += more.x; add.y += more.y; add.z += more.z; add.w += more.w;
+            }
           }
           z.x += add.x; z.y += add.y; z.z += add.z; z.w += add.w;
           store4f(r + 4 * gi, z);
@@ -318,9 +336,20 @@ __device__ __forceinline__ void load8w(const float* p, float (&v)[8]) {
   }
 }
 
+// 8 consecutive floats from a 16-byte aligned address
+__device__ __forceinline__ void load8a(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
 // grid (tokens, parts): the blocks of a token split its heads between them;
 // with the per-layer norm every block sums the whole q and k rows itself (a
 // few KB from L2) so that no block waits for another.
+// EAGER (few tokens): every input of a work item is fetched before any arithmetic, the
+// norm weights, cos and sin without an alignment branch between them (the host checks their
+// bases); with many tokens the registers that takes cost occupancy (33 -> 39 us at 2,048).
+template <bool EAGER>
 __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
   extern __shared__ float head_inv[];
   __shared__ float scratch[66];
@@ -393,6 +422,51 @@ __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
     if (a.norm_mode == 1) inv = is_q ? inv_q : inv_k;
     if (a.norm_mode == 2) inv = head_inv[is_q ? h : a.nq + h];
     const int wbase = a.norm_mode == 1 ? h * d : 0;
+    if (EAGER) {
+      if (ci < hc) {
+        const int i0 = ci * 8, i1 = i0 + half;
+        const uint4 r0 = *reinterpret_cast<const uint4*>(src + i0), r1 = *reinterpret_cast<const uint4*>(src + i1);
+        float w0[8], w1[8], c[8], sn[8];
+        if (a.norm_mode) {
+          load8a(nw + wbase + i0, w0);
+          load8a(nw + wbase + i1, w1);
+        }
+        if (cs) {
+          load8a(cs + i0, c);
+          load8a(cs + half + i0, sn);
+        }
+        Chunk8 x0 = unpack8(r0), x1 = unpack8(r1);
+        if (a.norm_mode) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            x0.v[i] = x0.v[i] * inv * (w0[i] + one);
+            x1.v[i] = x1.v[i] * inv * (w1[i] + one);
+          }
+        }
+        Chunk8 y0 = x0, y1 = x1;
+        if (cs) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            y0.v[i] = x0.v[i] * c[i] - x1.v[i] * sn[i];
+            y1.v[i] = x1.v[i] * c[i] + x0.v[i] * sn[i];
+          }
+        }
+        store8(dst + i0, y0);
+        store8(dst + i1, y1);
+      } else {
+        const int i0 = (ci + hc) * 8;               // pieces beyond the rotary span
+        const uint4 r0 = *reinterpret_cast<const uint4*>(src + i0);
+        float w0[8];
+        if (a.norm_mode) load8a(nw + wbase + i0, w0);
+        Chunk8 x0 = unpack8(r0);
+        if (a.norm_mode) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x0.v[i] = x0.v[i] * inv * (w0[i] + one);
+        }
+        store8(dst + i0, x0);
+      }
+      continue;
+    }
     if (ci < hc) {
       const int i0 = ci * 8, i1 = i0 + half;
       Chunk8 x0 = load8(src + i0), x1 = load8(src + i1);
@@ -553,7 +627,11 @@ int ft_rmsnorm(const void* delta, float* residual, const float* weight, void* ou
   // 16-byte pieces when the row allows it and fits the registers kept between the passes
   const bool vec = !(H & 3) && H <= 4 * NORM_THREADS * NORM_KEEP && !((uintptr_t)delta & 15) &&
                    !((uintptr_t)residual & 15) && !((uintptr_t)weight & 15) && !((uintptr_t)out & 15);
-  if (vec) {
+  if (vec && T <= ROW_KERNEL_EAGER_TOKENS) {
+    FT_DISPATCH(dtype, AT,
+                (launch_pdl(rmsnorm_kernel<AT, true, true>, dim3(T), dim3(NORM_THREADS), 0, stream,
+                            (const AT*)delta, residual, weight, (AT*)out, H, eps, plus_one, k)));
+  } else if (vec) {
     FT_DISPATCH(dtype, AT,
                 launch_pdl(rmsnorm_kernel<AT, true>, dim3(T), dim3(NORM_THREADS), 0, stream,
                            (const AT*)delta, residual, weight, (AT*)out, H, eps, plus_one, k));
@@ -587,7 +665,10 @@ int ft_qk_rope_store(const void* qkv, void* q_out, void* kv_pages, const float* 
     int parts = T >= 512 ? 1 : (pieces + 255) / 256;
     if (parts > 8) parts = 8;
     if (parts < 1) parts = 1;
-    launch_pdl(qk_rope_store_vec_kernel, dim3(T, parts), dim3(256), smem, stream, a);
+    const bool eager = T <= ROW_KERNEL_EAGER_TOKENS && !((uintptr_t)q_weight & 15) && !((uintptr_t)k_weight & 15) &&
+                       !((uintptr_t)cos_sin & 15);
+    if (eager) launch_pdl(qk_rope_store_vec_kernel<true>, dim3(T, parts), dim3(256), smem, stream, a);
+    else launch_pdl(qk_rope_store_vec_kernel<false>, dim3(T, parts), dim3(256), smem, stream, a);
     FT_LAUNCH_CHECK();
     return FT_OK;
   }
