@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(128) router_logits_kernel(const AT* __restrict
   float acc[TT];
 #pragma unroll
   for (int i = 0; i < TT; ++i) acc[i] = 0.f;
-#pragma unroll 2
+#pragma unroll 4
   for (int h = warp * 256 + lane * 8; h < H; h += 1024) {
     float wv[8];
     load8f(w + h, wv);
