@@ -197,3 +197,33 @@ def test_trace_run_tool(models, expected, tmp_path, dtype):
             assert torch.equal(same[rid], got[rid]), "the tool and the in-process engine differ"
         want = plain_logits(models, which, dtype, reqs, routing)
     compare(got, want, dtype, "trace_run mixed")
+
+
+def test_decode_batch_on_the_tcgen05_experts_replays_like_it_runs(models, monkeypatch):
+    """Twelve requests decoding together on tiny-A: more than four routes per expert, so the
+    experts run on the tcgen05 grouped GEMM (tile list, gather and both products inside the
+    captured graph).  The replayed steps must give the bits of the eagerly run ones."""
+    from freetoken_b200.csrc import ops
+    from freetoken_b200.engine import Engine, EngineArgs, StepEntry
+    calls = []
+    real = ops.moe_experts_tc
+    monkeypatch.setattr(ops, "moe_experts_tc", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    vocab = tiny.TINY_A["vocab_size"]
+    ids = [f"r{i}" for i in range(12)]
+    prompts = [tiny.tokens(20 + i, 3 + i, vocab) for i in range(12)]
+    steps = [[int(t) for t in tiny.tokens(40 + s, 12, vocab)] for s in range(6)]
+
+    def run(max_bs):
+        engine = Engine.from_folder(models["A"], EngineArgs(dtype="bfloat16", page_size=4, num_pages=128,
+                                                            max_running_requests=12, cuda_graph_max_bs=max_bs))
+        engine.step([StepEntry(r, p, []) for r, p in zip(ids, prompts)])
+        out = [engine.step([StepEntry(r, [tok], [0]) for r, tok in zip(ids, toks)]).float().cpu() for toks in steps]
+        ops.check_tc_status(engine.device)
+        return out, engine.graph_replays
+
+    eager, none = run(0)
+    assert none == 0 and calls, "the grouped GEMM never ran"
+    replayed, replays = run(64)
+    assert replays >= 4
+    for a, b in zip(eager, replayed):
+        assert torch.equal(a, b)
