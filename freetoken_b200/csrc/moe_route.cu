@@ -413,10 +413,17 @@ __global__ void __launch_bounds__(1024) moe_chunk_scan_kernel(int* __restrict__ 
     const int e = base + threadIdx.x;
     int total = 0;
     if (e < E) {
-      for (int c = 0; c < chunks; ++c) {
-        const int v = chunk_counts[(size_t)c * E + e];
-        chunk_counts[(size_t)c * E + e] = total;
-        total += v;
+      // eight chunks' counts are fetched together (one after the other, each behind the
+      // store before it, the loads were this kernel's whole time), then turned into prefixes
+      for (int c0 = 0; c0 < chunks; c0 += 8) {
+        int v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = c0 + u < chunks ? chunk_counts[(size_t)(c0 + u) * E + e] : 0;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (c0 + u < chunks) chunk_counts[(size_t)(c0 + u) * E + e] = total;
+          total += v[u];
+        }
       }
       counts[e] = total;
     }
