@@ -18,6 +18,16 @@
 
 namespace ft {
 
+// 4 consecutive elements as float32
+__device__ __forceinline__ float4 load4f(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4f(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+
 // ---------------------------------------------------------------- embedding
 template <typename WT>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
@@ -29,6 +39,12 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __res
   if (id < 0 || id >= vocab) id = 0;  // validated on the host; never index outside the table
   const WT* row = table + (size_t)id * H;
   float* out = residual + (size_t)t * H;
+  // four elements a step where the row allows it (8-byte loads of bfloat16, 16-byte stores)
+  if ((H & 3) == 0 && (((uintptr_t)table | (uintptr_t)residual) & 15) == 0 && (H * sizeof(WT)) % 16 == 0) {
+    for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x)
+      *reinterpret_cast<float4*>(out + 4 * i) = load4f(row + 4 * i);
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_float(row[i]);
 }
 
@@ -41,14 +57,6 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __res
 constexpr int NORM_THREADS = 512;
 constexpr int NORM_KEEP = 4;
 
-__device__ __forceinline__ float4 load4f(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 load4f(const __nv_bfloat16* p) {
-  const uint2 raw = *reinterpret_cast<const uint2*>(p);
-  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-  return make_float4(a.x, a.y, b.x, b.y);
-}
-__device__ __forceinline__ void store4f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
 __device__ __forceinline__ void store4f(__nv_bfloat16* p, float4 v) {
   uint2 raw;
   *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
