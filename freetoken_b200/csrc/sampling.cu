@@ -58,17 +58,21 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   const float* x = logits + (size_t)row * V;
   const float T = temperature ? temperature[row] : 0.f;
 
+  // one pass: a thread walks its indices in ascending order, so a strictly larger value
+  // keeps the first index that holds the thread's maximum
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, x[i]);
+  int best = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = x[i];
+    if (v > mx) { mx = v; best = i; }
+  }
+  const float mine = mx;
   mx = block_max_f(mx, scratch);
 
   if (!(T > 0.f)) {
     if (threadIdx.x == 0) winner = 0x7fffffff;
     __syncthreads();
-    int best = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x)
-      if (x[i] == mx && i < best) best = i;
-    if (best != 0x7fffffff) atomicMin(&winner, best);
+    if (mine == mx && best != 0x7fffffff) atomicMin(&winner, best);
     __syncthreads();
     if (threadIdx.x == 0) out[row] = winner == 0x7fffffff ? 0 : winner;
     return;
